@@ -1,0 +1,114 @@
+/*
+ * ri_b200.h — C ABI of libri_b200.so: wave-index decode attention for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every function returns 0 on success or a negative ri_status; ri_last_error() gives the
+ *    message of the calling thread's last failure.
+ *  - Pointers named d_* are device pointers, h_* host pointers; the caller owns every buffer.
+ *  - No function allocates device memory or synchronises the device unless it says so.
+ *  - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *  - Element type `dtype`: RI_BF16 or RI_F16 (16-bit storage, fp32 accumulation).
+ *  - G = batch * kv_heads "groups"; gs = q_heads / kv_heads (<= 8); head_dim is 128.
+ *
+ * Each entry cites the reference interface it replaces (paths inside the reference project).
+ */
+#ifndef RI_B200_H
+#define RI_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ri_status {
+  RI_OK = 0,
+  RI_ERR_INVALID = -1,   /* bad argument (null pointer, unsupported size or dtype) */
+  RI_ERR_CUDA = -2,      /* a CUDA runtime call or launch failed */
+  RI_ERR_TIMEOUT = -3,   /* a bounded device-side wait ran out */
+  RI_ERR_STATE = -4      /* call order violated (e.g. update before access) */
+} ri_status;
+
+enum { RI_BF16 = 0, RI_F16 = 1 };
+enum { RI_HEAD_DIM = 128 };
+
+const char* ri_last_error(void);
+int ri_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused decode path (all clusters resident in HBM in cluster-contiguous order).
+ * Replaces, per layer and decode step, the whole body of
+ * cache_hub/retroinfer_cache.py:549-697 (`retroinfer_cache.compute`):
+ * batch_gemm_softmax + sum/masked_fill/topk (:569-575), gather_copy_vectors (:601-605),
+ * weighted_flash_decoding on the estimation zone (:611-617), the page-budget rule of
+ * WaveBufferCPU::batch_access (wave_buffer_cpu.cpp:207-216), gather_copy_and_concat
+ * (:642-648) and the merging weighted_flash_decoding (:666-674).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ri_wave_layer {
+  /* geometry */
+  int32_t groups;            /* G */
+  int32_t group_size;        /* gs, 1..8 */
+  int32_t n_centroids;       /* C (multiple of 8, <= 65535) */
+  int32_t nprobe;            /* P: clusters attended exactly */
+  int32_t n_estimate;        /* E: clusters approximated by their centroid */
+  int32_t page_size;         /* tokens per page (reference: cache_unit_size = 8) */
+  int32_t buffer_pages;      /* page budget per group for retrieved clusters */
+  int32_t dtype;             /* RI_BF16 / RI_F16 */
+  int64_t tokens_per_group;  /* N: rows of d_keys/d_values per group */
+  int32_t steady_stride;     /* rows allocated per group in the steady zone */
+  int32_t max_exact_rows;    /* capacity of d_rows per group (>= buffer_pages*page_size) */
+  /* meta index (cache_hub/retroinfer_cache.py:212-227) */
+  const void* d_centroids;       /* [G, C, 128] */
+  const void* d_value_sum;       /* [G, C, 128] */
+  const void* d_cluster_size;    /* [G, C] in `dtype` (the reference stores sizes in the KV dtype, :432) */
+  const int32_t* d_cluster_count;  /* [G, C] exact sizes; 0 marks an empty (masked) cluster */
+  const int32_t* d_cluster_offset; /* [G, C+1] first row of each cluster in d_keys/d_values */
+  /* cluster-contiguous KV (the reference's list_keys/list_values, :264-274, kept in HBM) */
+  const void* d_keys;            /* [G, N, 128] */
+  const void* d_values;          /* [G, N, 128] */
+  /* steady zone (:83-92) and its current length for this layer (:559), read on the device */
+  const void* d_steady_keys;     /* [G, steady_stride, 128] */
+  const void* d_steady_values;
+  const int32_t* d_static_len;   /* [1] */
+  /* query and output */
+  const void* d_q;               /* [G, gs, 128]  (== [B, 1, Hq, 128]) */
+  void* d_out;                   /* [G, gs, 128] */
+  /* scratch owned by the caller, sizes from ri_wave_scratch_bytes(); reusable across layers */
+  void* d_scratch;
+  /* optional outputs (may be NULL) */
+  int64_t* d_retrieved_ids;      /* [G, P] ranked cluster ids (reference: cluster_ids, :575) */
+  int32_t* d_retrieved_kept;     /* [G] how many of them fit the page budget */
+  int64_t* d_estimated_ids;      /* [G, E] */
+} ri_wave_layer;
+
+/* Bytes of scratch one ri_wave_decode_layer call needs for this geometry (no device work). */
+int64_t ri_wave_scratch_bytes(const ri_wave_layer* p);
+
+/* Launch scan + select + attend for one layer on `stream`.  The scratch must have been
+ * zero-filled once before its first use (the kernels leave it reusable). */
+int ri_wave_decode_layer(const ri_wave_layer* p, void* stream);
+
+/* The three stages on their own (same parameter block), for tests and profiling. */
+int ri_wave_scan(const ri_wave_layer* p, void* stream);    /* q.C^T scores -> scratch */
+int ri_wave_select(const ri_wave_layer* p, void* stream);  /* softmax, group sum, top-k split */
+int ri_wave_attend(const ri_wave_layer* p, void* stream);  /* weighted split-K flash decoding */
+
+/* Views into the scratch (device pointers valid after ri_wave_select), for tests. */
+typedef struct ri_wave_views {
+  const float* d_scores;        /* [G, gs, C] alpha*q.c in fp32 */
+  const uint16_t* d_dist_keys;  /* [G, C] order-preserving 16-bit key of the group distance */
+  const int32_t* d_exact_rows;  /* [G, max_exact_rows] */
+  const int32_t* d_n_exact;     /* [G] retrieved rows (without the steady zone) */
+} ri_wave_views;
+int ri_wave_scratch_views(const ri_wave_layer* p, ri_wave_views* out);
+
+/* Append this step's key/value to the steady zone at row *d_position.
+ * Replaces cache_hub/retroinfer_cache.py:538-540 (`decode_update_kv_cache`).
+ * d_k/d_v: [G, 128] (== [B, 1, Hk, 128]); steady tensors [G, steady_stride, 128]. */
+int ri_steady_append(const void* d_k, const void* d_v, void* d_steady_keys, void* d_steady_values,
+                     const int32_t* d_position, int32_t groups, int32_t steady_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RI_B200_H */

@@ -1,0 +1,87 @@
+// Shared helpers for libri_b200: error reporting, 16-bit element traits, warp-level MMA.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ri_b200.h"
+
+// ---- error reporting (ri_error.cu) ---------------------------------------------------------
+int ri_fail(int status, const char* fmt, ...);
+
+#define RI_REQUIRE(cond, ...)                                  \
+  do {                                                         \
+    if (!(cond)) return ri_fail(RI_ERR_INVALID, __VA_ARGS__);  \
+  } while (0)
+
+#define RI_CUDA_OK(expr)                                                                   \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess)                                                                \
+      return ri_fail(RI_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                     __FILE__, __LINE__);                                                  \
+  } while (0)
+
+#define RI_LAUNCH_OK(name)                                                                        \
+  do {                                                                                            \
+    cudaError_t e__ = cudaGetLastError();                                                         \
+    if (e__ != cudaSuccess)                                                                       \
+      return ri_fail(RI_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__));      \
+  } while (0)
+
+static inline int64_t ri_align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+__host__ __device__ constexpr size_t ri_align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+// ---- 16-bit element traits -----------------------------------------------------------------
+// DT = RI_BF16 (0) or RI_F16 (1).  Storage is 16 bits, all arithmetic accumulates in fp32.
+template <int DT>
+struct Elem;
+
+template <>
+struct Elem<RI_BF16> {
+  __device__ __forceinline__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  __device__ __forceinline__ static uint16_t bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
+  __device__ __forceinline__ static float from_bits(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+  __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                  uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+template <>
+struct Elem<RI_F16> {
+  __device__ __forceinline__ static float round(float x) { return __half2float(__float2half_rn(x)); }
+  __device__ __forceinline__ static uint16_t bits(float x) { return __half_as_ushort(__float2half_rn(x)); }
+  __device__ __forceinline__ static float from_bits(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+  __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                  uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+// Order-preserving map of a 16-bit float pattern onto uint16 (larger float -> larger key).
+__device__ __forceinline__ uint16_t ri_ordered_key(uint16_t b) {
+  return (b & 0x8000u) ? (uint16_t)~b : (uint16_t)(b | 0x8000u);
+}
+
+__device__ __forceinline__ uint4 ri_ldg16(const uint4* p) { return __ldg(p); }
+
+constexpr float RI_LOG2E = 1.4426950408889634f;

@@ -1,0 +1,160 @@
+"""Parity of the fused decode path (scan -> select -> attend, through the C ABI) against the
+CPU oracle on the same seeded inputs.
+
+Bars: centroid scores within fp32 accumulation noise; distance keys and selected sets bit-exact
+except where distances tie within 1e-3 of the cut; attention output max-abs <= 2e-2 and
+mean-abs <= 2e-3 against the oracle's fp32 evaluation."""
+import pytest
+import torch
+
+from helpers import Case, build_cpu_index, queries, to_gpu_layer, SINK, RECENT
+from oracle import attention as oat
+from oracle import score_select as oss
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    "small_gs4": Case(2, 2, 4, 2048 + 68, 128, 1, 6, 30),
+    "qwen_gs7": Case(1, 2, 7, 1536 + 68, 96, 2, 5, 22, seed=3),
+    "gs8_planted": Case(2, 1, 8, 2048 + 68, 128, 4, 6, 29, seed=4, planted=16),
+    "gs1": Case(1, 3, 1, 1024 + 68, 64, 1, 4, 15, seed=5),
+    "no_estimation": Case(1, 2, 4, 1024 + 68, 64, 1, 4, 0, seed=6),
+    "tight_budget": Case(1, 2, 4, 2048 + 68, 64, 1, 8, 14, seed=7, buffer_pages=9),
+    "empty_clusters": Case(1, 2, 4, 1024 + 68, 64, 1, 4, 15, seed=8, duplicate_rows=37),
+    "cfg0_geometry": Case(1, 8, 4, 8192, 512, 1, 9, 118, seed=0, iters=3),
+}
+
+
+def run_oracle(case, cpu, q, static_len):
+    return oat.compute(q, cpu["centroids"], cpu["value_sum"], cpu["cluster_size"], cpu["mask"],
+                       cpu["cluster_count"], cpu["cluster_offset"], cpu["keys"], cpu["values"],
+                       cpu["steady_keys"], cpu["steady_values"], static_len, case.nprobe,
+                       case.nprobe + case.n_estimate, case.page_size, case.pages(), return_parts=True)
+
+
+def ordered_key(dist: torch.Tensor) -> torch.Tensor:
+    bits = dist.view(torch.int16).to(torch.int32) & 0xFFFF
+    return torch.where(bits >= 0x8000, (~bits) & 0xFFFF, bits | 0x8000)
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fused_decode_matches_oracle(name):
+    case = CASES[name]
+    cpu = build_cpu_index(case)
+    static_len = SINK + RECENT + 1
+    # one generated token already appended
+    cpu["steady_keys"][:, SINK + RECENT] = torch.randn((case.groups, 128)).to(case.dtype)
+    cpu["steady_values"][:, SINK + RECENT] = torch.randn((case.groups, 128)).to(case.dtype)
+    layer = to_gpu_layer(case, cpu, static_len)
+    q = queries(case)
+    ref_out, parts = run_oracle(case, cpu, q, static_len)
+
+    out = layer.compute(q.cuda())
+    torch.cuda.synchronize()
+    v = layer.views()
+
+    # scores: alpha * q.c in fp32
+    ref_scores = torch.bmm(q.reshape(case.groups, case.group_size, 128).float(),
+                           cpu["centroids"].float().transpose(1, 2)) / 128 ** 0.5
+    torch.testing.assert_close(v["scores"].cpu(), ref_scores, rtol=1e-4, atol=1e-3)
+
+    # 16-bit distance keys: bit-exact up to the rare rounding flip caused by fp32 summation order
+    keys = (v["dist_keys"].cpu().to(torch.int32) & 0xFFFF)
+    ref_keys = ordered_key(parts["dist"])
+    assert (keys != ref_keys).float().mean() < 0.02
+    assert ((keys - ref_keys).abs() <= 1).all()
+
+    # selected sets, with the tie rule
+    dist = parts["dist"]
+    ret = layer.retrieved_ids.cpu()
+    assert oss.selection_matches(dist, ret, case.nprobe)
+    if case.n_estimate:
+        both = torch.cat((ret, layer.estimated_ids.cpu()), dim=1)
+        assert oss.selection_matches(dist, both, case.nprobe + case.n_estimate)
+    # ranking of the retrieved clusters is descending
+    d_ret = torch.gather(dist.float(), 1, ret)
+    assert (d_ret[:, :-1] >= d_ret[:, 1:] - 1e-3).all()
+
+    # page-budget rule on the kernel's own ranking
+    kept = layer.retrieved_kept.cpu()
+    for g in range(case.groups):
+        expect = oat.surviving_clusters(ret[g], cpu["cluster_count"][g], case.page_size, case.pages())
+        assert int(kept[g]) == expect
+        rows = []
+        for cid in ret[g, :expect].tolist():
+            rows.extend(range(int(cpu["cluster_offset"][g, cid]), int(cpu["cluster_offset"][g, cid + 1])))
+        assert int(v["n_exact"][g]) == len(rows)
+        assert v["exact_rows"][g, :len(rows)].cpu().tolist() == rows
+
+    # attention output
+    err = (out.cpu().float() - ref_out.float()).abs()
+    assert err.max() <= 2e-2, f"max abs err {err.max():.4f}"
+    assert err.mean() <= 2e-3, f"mean abs err {err.mean():.5f}"
+
+
+def test_tight_budget_actually_cuts():
+    case = CASES["tight_budget"]
+    cpu = build_cpu_index(case)
+    layer = to_gpu_layer(case, cpu, SINK + RECENT)
+    layer.compute(queries(case).cuda())
+    torch.cuda.synchronize()
+    assert (layer.retrieved_kept.cpu() < case.nprobe).any()
+
+
+def test_empty_clusters_rank_last():
+    case = CASES["empty_clusters"]
+    cpu = build_cpu_index(case)
+    assert int(cpu["mask"].sum()) > 0
+    layer = to_gpu_layer(case, cpu, SINK + RECENT)
+    layer.compute(queries(case).cuda())
+    torch.cuda.synchronize()
+    ret = layer.retrieved_ids.cpu()
+    nonempty = (~cpu["mask"]).sum(1)
+    for g in range(case.groups):
+        if nonempty[g] >= case.nprobe:
+            assert not cpu["mask"][g, ret[g]].any()
+
+
+def test_repeatable_and_scratch_reusable():
+    """Two calls in a row on the same scratch give bit-identical results (the combine
+    counters are left at zero, the selection is deterministic)."""
+    case = CASES["small_gs4"]
+    cpu = build_cpu_index(case)
+    layer = to_gpu_layer(case, cpu, SINK + RECENT)
+    q = queries(case).cuda()
+    a = layer.compute(q).clone()
+    b = layer.compute(q).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def test_steady_append_and_growing_static_len():
+    from retrievalattention_b200 import wave
+
+    case = CASES["small_gs4"]
+    cpu = build_cpu_index(case)
+    layer = to_gpu_layer(case, cpu, SINK + RECENT)
+    pos = layer.t["static_len"]
+    q = queries(case, seed=7)
+    for step in range(3):
+        k_new = torch.randn((case.batch, 1, case.kv_heads, 128)).to(case.dtype)
+        v_new = torch.randn((case.batch, 1, case.kv_heads, 128)).to(case.dtype)
+        wave.steady_append(k_new.cuda(), v_new.cuda(), layer.t["steady_keys"], layer.t["steady_values"], pos)
+        cpu["steady_keys"][:, SINK + RECENT + step] = k_new.reshape(case.groups, 128)
+        cpu["steady_values"][:, SINK + RECENT + step] = v_new.reshape(case.groups, 128)
+        pos += 1
+        static_len = SINK + RECENT + step + 1
+        out = layer.compute(q.cuda())
+        ref_out, _ = run_oracle(case, cpu, q, static_len)
+        err = (out.cpu().float() - ref_out.float()).abs()
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3
+    assert torch.equal(layer.t["steady_keys"].cpu(), cpu["steady_keys"])
+
+
+def test_invalid_arguments_are_rejected():
+    import ctypes as C
+    from retrievalattention_b200 import _lib
+
+    p = _lib.WaveLayer()
+    assert _lib.lib.ri_wave_decode_layer(C.byref(p), None) == -1
+    assert b"groups" in _lib.lib.ri_last_error()
