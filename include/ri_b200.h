@@ -88,6 +88,20 @@ int64_t ri_wave_scratch_bytes(const ri_wave_layer* p);
  * zero-filled once before its first use (the kernels leave it reusable). */
 int ri_wave_decode_layer(const ri_wave_layer* p, void* stream);
 
+/* Same work as ri_wave_decode_layer for callers that cannot allocate device memory at all: an
+ * inference server that gave all of HBM to its own pool at start-up, or a decode loop that must
+ * not call cudaMalloc/cudaFree because those stall the whole device.  `p->d_scratch` is ignored;
+ * the scratch is a fixed RI_WAVE_STATIC_SCRATCH_BYTES array inside the library image, set aside
+ * on every GPU that loads the library until the process exits.  Geometries that need more are
+ * refused with RI_ERR_INVALID (config 1 of the benchmark, 32 groups x 8192 centroids, needs
+ * about 12 MB).  The call allocates nothing; it clears the part of the array that must start at
+ * zero on `stream` and otherwise finds the previous call's leftovers.  All calls share the one
+ * array, so calls whose GPU work overlaps (other streams, unordered threads) race: order them.
+ * The first call on each device looks up the array's device address; make it at start-up,
+ * before any stream capture.  This entry point has no counterpart in the reference. */
+#define RI_WAVE_STATIC_SCRATCH_BYTES (16u << 20)
+int ri_wave_decode_layer_static(const ri_wave_layer* p, void* stream);
+
 /* The three stages on their own (same parameter block), for tests and profiling. */
 int ri_wave_scan(const ri_wave_layer* p, void* stream);    /* q.C^T scores -> scratch */
 int ri_wave_select(const ri_wave_layer* p, void* stream);  /* softmax, group sum, top-k split */

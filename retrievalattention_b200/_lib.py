@@ -47,7 +47,8 @@ def _load() -> C.CDLL:
     lib.ri_version.restype = C.c_int
     lib.ri_wave_scratch_bytes.restype = C.c_int64
     lib.ri_wave_scratch_bytes.argtypes = [C.POINTER(WaveLayer)]
-    for name in ("ri_wave_decode_layer", "ri_wave_scan", "ri_wave_select", "ri_wave_attend"):
+    for name in ("ri_wave_decode_layer", "ri_wave_decode_layer_static", "ri_wave_scan", "ri_wave_select",
+                 "ri_wave_attend"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]

@@ -114,6 +114,19 @@ class WaveIndexLayer:
         _lib.check(_lib.lib.ri_wave_decode_layer(C.byref(self.params), _lib.current_stream()), "ri_wave_decode_layer")
         return out
 
+    def compute_static(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``compute`` without caller scratch, for hosts that must not allocate device memory (a
+        server whose pool already owns all of HBM, or a loop that bans cudaMalloc because it stalls
+        the device).  Uses the library's built-in 16 MiB scratch; larger geometries raise.  All
+        calls share that array: do not let two of them overlap on the GPU.  Call it once at
+        start-up, outside stream capture, so the array's address is resolved."""
+        if out is None:
+            out = torch.empty_like(q)
+        self._bind(q, out)
+        _lib.check(_lib.lib.ri_wave_decode_layer_static(C.byref(self.params), _lib.current_stream()),
+                   "ri_wave_decode_layer_static")
+        return out
+
     def stage(self, name: str, q: torch.Tensor, out: torch.Tensor) -> None:
         """Run one stage alone (``scan``/``select``/``attend``) — tests and profiling."""
         self._bind(q, out)
