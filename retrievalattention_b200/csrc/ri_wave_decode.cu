@@ -599,18 +599,58 @@ __global__ void __launch_bounds__(128) wave_attend_kernel(AttendArgs a) {
   if (!s_last) return;
   __threadfence();
   const int64_t gbase = (int64_t)g * a.n_chunks;
-  for (int h = 0; h < gs; ++h) {
+  // All loads below are independent of one another, so the whole merge costs a few L2 round
+  // trips instead of one per chunk.  Tables (n_active <= 256 rows of 8 heads) reuse sm_o.
+  float* tf = &sm_o[0][0][0];                 // running max, then the rescale factor 2^(m - M)
+  float* tl = tf + 256 * kMaxHeads;           // denominators
+  for (int i = tid; i < n_active * kMaxHeads; i += 128) {
+    tf[i] = __ldcg(a.part_m + gbase * kMaxHeads + i);
+    tl[i] = __ldcg(a.part_l + gbase * kMaxHeads + i);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {            // warp w reduces heads 2w and 2w+1
+    const int h = warp * 2 + hh;
     float M = -INFINITY;
-    for (int c = 0; c < n_active; ++c) M = fmaxf(M, __ldcg(a.part_m + (gbase + c) * kMaxHeads + h));
+    for (int c = lane; c < n_active; c += 32) M = fmaxf(M, tf[c * kMaxHeads + h]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     const float Ms = M == -INFINITY ? 0.f : M;
-    float L = 0.f, O = 0.f;
-    for (int c = 0; c < n_active; ++c) {
-      const float f = exp2f(__ldcg(a.part_m + (gbase + c) * kMaxHeads + h) - Ms);
-      L += __ldcg(a.part_l + (gbase + c) * kMaxHeads + h) * f;
-      O += __ldcg(a.part_o + ((gbase + c) * gs + h) * RI_HEAD_DIM + tid) * f;
+    float L = 0.f;
+    for (int c = lane; c < n_active; c += 32) {
+      const float f = exp2f(tf[c * kMaxHeads + h] - Ms);
+      tf[c * kMaxHeads + h] = f;
+      L += tl[c * kMaxHeads + h] * f;
     }
-    const float res = L > 0.f ? O / L : 0.f;
-    reinterpret_cast<uint16_t*>(a.out)[((int64_t)g * gs + h) * RI_HEAD_DIM + tid] = Elem<DT>::bits(res);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) sm_l[0][h] = L;
+  }
+  __syncthreads();
+  const int dq = tid >> 2, cl = tid & 3;      // 4 channels per thread, chunks split 4 ways
+  for (int h = 0; h < gs; ++h) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int c = cl; c < n_active; c += 4) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_o + ((gbase + c) * gs + h) * RI_HEAD_DIM) + dq);
+      const float f = tf[c * kMaxHeads + h];
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+      acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+      acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+      acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    }
+    if (cl == 0) {
+      const float L = sm_l[0][h];
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+      uint2 o2;
+      o2.x = Elem<DT>::pack2(acc.x * inv, acc.y * inv);
+      o2.y = Elem<DT>::pack2(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + ((int64_t)g * gs + h) * RI_HEAD_DIM + 4 * dq) = o2;
+    }
   }
   if (tid == 0) a.counters[g] = 0u;   // leave the scratch reusable
 }
@@ -690,6 +730,7 @@ int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   a.est_chunks = L.est_chunks; a.n_chunks = L.n_chunks; a.steady_stride = p.steady_stride;
   a.max_rows = p.max_exact_rows;
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  RI_REQUIRE(L.n_chunks <= 256, "geometry needs %d attention chunks per group, the merge handles 256", L.n_chunks);
   dim3 grid(L.n_chunks, p.groups);
   wave_attend_kernel<DT><<<grid, 128, 0, s>>>(a);
   RI_LAUNCH_OK("wave_attend_kernel");
