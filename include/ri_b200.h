@@ -122,6 +122,49 @@ int ri_wave_scratch_views(const ri_wave_layer* p, ri_wave_views* out);
 int ri_steady_append(const void* d_k, const void* d_v, void* d_steady_keys, void* d_steady_values,
                      const int32_t* d_position, int32_t groups, int32_t steady_stride, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Prefill clustering.  Replaces cache_hub/kmeans.py:224-259 (`segment_k_means`: Triton assign,
+ * update, index-add and reverse-index kernels) and, with `center` = 1, also its caller's
+ * wrapping in cache_hub/retroinfer_cache.py:416-432 (mean-centring, centroid + mean, sizes in
+ * the KV dtype) and the CPU re-layout of K/V into cluster-contiguous order
+ * (wave_buffer_cpu.cpp:513-567, `parse_clusters` + `organize_kv`).
+ *
+ * Schedule: iterations 1..n_iters-1 run per segment (contiguous ranges of n_tokens/n_segments
+ * tokens with n_centroids/n_segments centroids each, tail tokens ignored) with L2-normalised
+ * centroids; the last iteration assigns every token against all centroids and takes the plain
+ * mean.  Assignment = arg-max inner product (first maximum wins).  Empty clusters keep their
+ * previous centroid, get a zero value sum and count 0.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ri_kmeans {
+  int32_t groups;        /* Z: independent (batch, kv-head) groups in this call */
+  int32_t n_tokens;      /* N rows per group */
+  int32_t n_centroids;   /* C; C/n_segments must be a multiple of 32 */
+  int32_t n_segments;
+  int32_t n_iters;       /* reference default 10 */
+  int32_t dtype;         /* RI_BF16 / RI_F16 */
+  int32_t center;        /* 0: d_keys are already centred (pure segment_k_means);
+                            1: subtract the per-group mean key first and add it back to the centroids */
+  int32_t reserved;
+  const void* d_keys;        /* [Z, N, 128] */
+  const void* d_values;      /* [Z, N, 128] */
+  void* d_centroids;         /* out [Z, C, 128] */
+  void* d_value_sum;         /* out [Z, C, 128] */
+  void* d_cluster_size;      /* out [Z, C] in `dtype` */
+  int32_t* d_cluster_count;  /* out [Z, C], may be NULL */
+  int32_t* d_cluster_offset; /* out [Z, C+1] exclusive prefix sums of the counts, may be NULL */
+  int32_t* d_assign;         /* out [Z, N] cluster of every token (reference: max_idx), may be NULL */
+  int32_t* d_order;          /* out [Z, N] token ids cluster by cluster, ascending inside a cluster
+                                (the reference's inverted lists, flattened), may be NULL */
+  void* d_keys_out;          /* out [Z, N, 128] K rows in d_order order, may be NULL (then no layout) */
+  void* d_values_out;        /* out [Z, N, 128] */
+  void* d_mean_key;          /* out [Z, 128] (only with center = 1), may be NULL */
+  void* d_scratch;           /* ri_kmeans_scratch_bytes() bytes, contents irrelevant */
+  int32_t* d_error;          /* out [1]: 1 if a device-side bounded wait ran out, may be NULL */
+} ri_kmeans;
+
+int64_t ri_kmeans_scratch_bytes(const ri_kmeans* p);
+int ri_kmeans_build(const ri_kmeans* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

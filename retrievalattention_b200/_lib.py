@@ -32,6 +32,19 @@ class WaveLayer(C.Structure):
     ]
 
 
+class KMeans(C.Structure):
+    """Mirror of ``struct ri_kmeans``."""
+
+    _fields_ = [
+        ("groups", C.c_int32), ("n_tokens", C.c_int32), ("n_centroids", C.c_int32), ("n_segments", C.c_int32),
+        ("n_iters", C.c_int32), ("dtype", C.c_int32), ("center", C.c_int32), ("reserved", C.c_int32),
+        ("d_keys", C.c_void_p), ("d_values", C.c_void_p), ("d_centroids", C.c_void_p), ("d_value_sum", C.c_void_p),
+        ("d_cluster_size", C.c_void_p), ("d_cluster_count", C.c_void_p), ("d_cluster_offset", C.c_void_p),
+        ("d_assign", C.c_void_p), ("d_order", C.c_void_p), ("d_keys_out", C.c_void_p), ("d_values_out", C.c_void_p),
+        ("d_mean_key", C.c_void_p), ("d_scratch", C.c_void_p), ("d_error", C.c_void_p),
+    ]
+
+
 class WaveViews(C.Structure):
     _fields_ = [("d_scores", C.c_void_p), ("d_dist_keys", C.c_void_p), ("d_exact_rows", C.c_void_p),
                 ("d_n_exact", C.c_void_p)]
@@ -54,6 +67,10 @@ def _load() -> C.CDLL:
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]
     lib.ri_wave_scratch_views.restype = C.c_int
     lib.ri_wave_scratch_views.argtypes = [C.POINTER(WaveLayer), C.POINTER(WaveViews)]
+    lib.ri_kmeans_scratch_bytes.restype = C.c_int64
+    lib.ri_kmeans_scratch_bytes.argtypes = [C.POINTER(KMeans)]
+    lib.ri_kmeans_build.restype = C.c_int
+    lib.ri_kmeans_build.argtypes = [C.POINTER(KMeans), C.c_void_p]
     lib.ri_steady_append.restype = C.c_int
     lib.ri_steady_append.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_int32, C.c_void_p]
     return lib

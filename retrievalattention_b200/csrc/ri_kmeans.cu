@@ -1,0 +1,743 @@
+// Prefill clustering: segmented inner-product Lloyd k-means, per-cluster value sums and the
+// cluster-contiguous KV layout.
+//
+//   centre   mean key per group (fp32 sums in a fixed order), centred = round(key - mean)
+//   assign   argmax_c <x, c> for every token of every problem: tcgen05 MMA (M = 128 tokens,
+//            N = 128 centroids, K = 128 channels as 8 x K16) with operands staged by TMA
+//            (128-byte swizzle) and fp32 accumulators in TMEM; a warp-specialised CTA
+//            (TMA producer / MMA issuer / 4 epilogue warps) overlaps the running arg-max of one
+//            accumulator buffer with the MMAs into the other.
+//   bucket   stable counting sort of the tokens of a problem by cluster: counts, offsets and
+//            the member list in ascending token order (deterministic, no global atomics).
+//   update   one warp per cluster sums its member rows in list order (fp32), forms the mean,
+//            optionally L2-normalises, and stores the centroid in the key dtype if the cluster
+//            is non-empty.  On the last iteration the same pass also produces the value sums
+//            and writes the cluster-contiguous copy of K and V.
+//
+// A "problem" is one (group, segment) pair during the segmented iterations and one group
+// during the last, global iteration (reference: cache_hub/kmeans.py:240-250).
+#include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "ri_common.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;       // tokens per CTA tile
+constexpr int kTileN = 128;       // centroids per MMA tile
+constexpr int kStages = 4;        // centroid-tile pipeline depth
+constexpr int kAssignThreads = 192;
+constexpr uint32_t kTmemCols = 256;   // two 128-column accumulator buffers
+constexpr int kHalfBytes = kTileM * 128;   // one K-block (64 channels) of a 128-row tile: 16 KB
+constexpr int kAssignSmem = 1024 /*align*/ + 2 * kHalfBytes /*A*/ + kStages * 2 * kHalfBytes /*B*/ + 256 /*barriers*/;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every spin-wait gives up after 2 s
+
+// ---- small PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: returns false (and raises the CTA's abort flag) if the barrier does not flip
+// within kWaitLimitNs or another role already gave up.
+// `where` (non-zero) identifies the wait in the error word that reaches the host.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) { *abort_flag = where; return false; }
+    }
+    if (spin > (1u << 28)) { *abort_flag = where + 100; return false; }   // second bound, independent of the timer
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 B (64 channels), 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  const uint64_t lo = (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16);            // LBO field = 1 (unused)
+  const uint64_t hi = (uint64_t)(1024 >> 4) | ((uint64_t)1 << 14) | ((uint64_t)2 << 29);      // SBO, version 1, SW128
+  return lo | (hi << 32);
+}
+
+// ---- assign ---------------------------------------------------------------------------------
+struct AssignArgs {
+  int32_t* assign;       // [total tokens] local centroid index of each token within its problem
+  int* error_flag;       // set to 1 if a bounded wait ran out
+  int n_tok;             // tokens per problem
+  int n_cen;             // centroids per problem
+  int seg_per_group;     // problems per group
+  int64_t group_stride;  // token rows per group (N)
+  uint32_t idesc;
+};
+
+__global__ void __launch_bounds__(kAssignThreads, 1)
+kmeans_assign_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_constant__ CUtensorMap map_cent,
+                     AssignArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // SW128 tiles need 1024-byte alignment
+  const uint32_t sA = base;
+  const uint32_t sB = base + 2 * kHalfBytes;
+  const uint32_t bars = sB + kStages * 2 * kHalfBytes;
+  const uint32_t bar_a_full = bars;
+  auto bar_b_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto bar_b_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 + 2 * kStages + b); };
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort, s_skip;
+
+  // once any CTA of this launch has given up, the rest leave at once (uniformly per CTA)
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(a.error_flag);
+  __syncthreads();
+  if (s_skip) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int problem = blockIdx.y;
+  const int tile = blockIdx.x;
+  const int64_t tok_row0 = (int64_t)(problem / a.seg_per_group) * a.group_stride +
+                           (int64_t)(problem % a.seg_per_group) * a.n_tok + (int64_t)tile * kTileM;
+  const int cen_row0 = problem * a.n_cen;
+  const int n_tiles = (a.n_cen + kTileN - 1) / kTileN;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(bar_a_full, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(bar_b_full(s), 1); mbar_init(bar_b_empty(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar_a_full, 2 * kHalfBytes);
+      tma_load_2d(sA, &map_keys, bar_a_full, 0, (int)tok_row0);
+      tma_load_2d(sA + kHalfBytes, &map_keys, bar_a_full, 64, (int)tok_row0);
+      int issued = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kStages;
+        if (!mbar_wait(bar_b_empty(s), ((j / kStages) & 1) ^ 1, abort_flag, 1)) break;
+        mbar_arrive_expect_tx(bar_b_full(s), 2 * kHalfBytes);
+        tma_load_2d(sB + s * 2 * kHalfBytes, &map_cent, bar_b_full(s), 0, cen_row0 + j * kTileN);
+        tma_load_2d(sB + s * 2 * kHalfBytes + kHalfBytes, &map_cent, bar_b_full(s), 64, cen_row0 + j * kTileN);
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        // give our own copies still in flight a bounded chance to land before the CTA exits
+        mbar_wait(bar_a_full, 0, abort_flag, 6);
+        for (int j = max(0, issued - kStages); j < issued; ++j)
+          mbar_wait(bar_b_full(j % kStages), (j / kStages) & 1, abort_flag, 7);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_a_full, 0, abort_flag, 2);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int s = j % kStages, buf = j & 1;
+        ok = mbar_wait(bar_b_full(s), (j / kStages) & 1, abort_flag, 3) &&
+             mbar_wait(bar_acc_empty(buf), ((j >> 1) & 1) ^ 1, abort_flag, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kTileN;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t da = umma_desc_sw128(sA + kb * kHalfBytes);
+          const uint64_t db = umma_desc_sw128(sB + s * 2 * kHalfBytes + kb * kHalfBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)   // K16 steps: 32 bytes along the swizzled row = +2 in the address field
+            tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, a.idesc, (kb | k) != 0);
+        }
+        tc_commit(bar_b_empty(s));     // the stage is free once these MMAs have read it
+        tc_commit(bar_acc_full(buf));  // and the accumulator is complete
+      }
+    }
+  } else {
+    // ---------------- epilogue: running arg-max over the centroid tiles ----------------
+    const int lane_group = warp & 3;                 // TMEM lanes 32*lane_group .. +31
+    const int row = lane_group * 32 + lane;
+    float best = -INFINITY;
+    int best_idx = 0;
+    bool ok = true;
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int buf = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(buf), (j >> 1) & 1, abort_flag, 5));   // warp-uniform
+      if (!ok) break;
+      tc_fence_after();
+      const int col0 = j * kTileN;
+      const int valid = min(kTileN, a.n_cen - col0);
+#pragma unroll 1
+      for (int ch = 0; ch < kTileN / 32; ++ch) {
+        uint32_t r[32];
+        tc_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * kTileN + ch * 32, r);
+        tc_wait_ld();
+        if (ch * 32 + 32 <= valid) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(r[i]);
+            if (v > best) { best = v; best_idx = col0 + ch * 32 + i; }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = __uint_as_float(r[i]);
+            if (ch * 32 + i < valid && v > best) { best = v; best_idx = col0 + ch * 32 + i; }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+    }
+    const int local_tok = tile * kTileM + row;
+    if (ok && local_tok < a.n_tok) a.assign[tok_row0 + row] = best_idx;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_abort) *a.error_flag = s_abort;   // which wait gave up (see mbar_wait call sites)
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+// ---- centre ---------------------------------------------------------------------------------
+constexpr int kMeanRows = 2048;   // rows per partial-sum CTA
+
+template <int DT>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const uint4* __restrict__ keys, float* __restrict__ partial,
+                                                             int n_tok, int chunks) {
+  const int z = blockIdx.y, chunk = blockIdx.x;
+  const int piece = threadIdx.x & 15, rl = threadIdx.x >> 4;   // 16 pieces of 8 channels x 16 row lanes
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int r0 = chunk * kMeanRows, r1 = min(n_tok, r0 + kMeanRows);
+  for (int r = r0 + rl; r < r1; r += 16) {
+    const uint4 v = ri_ldg16(keys + ((int64_t)z * n_tok + r) * 16 + piece);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += Elem<DT>::from_bits((uint16_t)(w[i] & 0xffffu));
+      acc[2 * i + 1] += Elem<DT>::from_bits((uint16_t)(w[i] >> 16));
+    }
+  }
+  __shared__ float red[16][128];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rl][piece * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) s += red[k][threadIdx.x];
+    partial[((int64_t)z * chunks + chunk) * 128 + threadIdx.x] = s;
+  }
+}
+
+template <int DT>
+__global__ void colmean_final_kernel(const float* __restrict__ partial, uint16_t* __restrict__ mean, int n_tok, int chunks) {
+  const int z = blockIdx.x, c = threadIdx.x;
+  float s = 0.f;
+  for (int k = 0; k < chunks; ++k) s += partial[((int64_t)z * chunks + k) * 128 + c];
+  mean[z * 128 + c] = Elem<DT>::bits(s / (float)n_tok);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) centre_apply_kernel(const uint4* __restrict__ keys, const uint16_t* __restrict__ mean,
+                                                           uint4* __restrict__ out, int64_t pieces_per_group) {
+  const int z = blockIdx.y;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pieces_per_group) return;
+  const int piece = (int)(i & 15);
+  const uint4 v = ri_ldg16(keys + (int64_t)z * pieces_per_group + i);
+  const uint4 m = *reinterpret_cast<const uint4*>(mean + z * 128 + piece * 8);
+  const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, mw[4] = {m.x, m.y, m.z, m.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float lo = Elem<DT>::from_bits((uint16_t)(vw[k] & 0xffffu)) - Elem<DT>::from_bits((uint16_t)(mw[k] & 0xffffu));
+    const float hi = Elem<DT>::from_bits((uint16_t)(vw[k] >> 16)) - Elem<DT>::from_bits((uint16_t)(mw[k] >> 16));
+    ow[k] = Elem<DT>::pack2(lo, hi);
+  }
+  out[(int64_t)z * pieces_per_group + i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+// ---- initial centroids (cache_hub/kmeans.py:234-237: index arithmetic in float32) -------------
+__global__ void init_centroids_kernel(const uint4* __restrict__ centred, uint4* __restrict__ cent, int n_tok, int n_cen,
+                                      float step, float half) {
+  const int z = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece
+  if (i >= n_cen * 16) return;
+  const int c = i >> 4, piece = i & 15;
+  const long long idx = (long long)__fadd_rn(__fmul_rn((float)c, step), half);
+  const long long row = idx < 0 ? 0 : (idx >= n_tok ? n_tok - 1 : idx);
+  cent[((int64_t)z * n_cen + c) * 16 + piece] = ri_ldg16(centred + ((int64_t)z * n_tok + row) * 16 + piece);
+}
+
+// ---- bucket ---------------------------------------------------------------------------------
+struct BucketArgs {
+  const int32_t* assign;   // [total tokens] local centroid ids
+  int32_t* order;          // [total tokens] local token ids, cluster-major, ascending inside a cluster
+  int32_t* count;          // [problems, n_cen]
+  int32_t* offset;         // [problems, n_cen + 1]
+  int n_tok, n_cen, seg_per_group;
+  int64_t group_stride;
+};
+
+__global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a) {
+  extern __shared__ int32_t cursor[];   // [n_cen]: counts, then running write positions
+  __shared__ uint32_t warp_sums[32];
+  __shared__ uint32_t s_carry;
+  const int problem = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t tok0 = (int64_t)(problem / a.seg_per_group) * a.group_stride + (int64_t)(problem % a.seg_per_group) * a.n_tok;
+  const int32_t* asg = a.assign + tok0;
+  for (int c = tid; c < a.n_cen; c += 1024) cursor[c] = 0;
+  if (tid == 0) s_carry = 0;
+  __syncthreads();
+  auto clamp_id = [&](int32_t c) { return min(max(c, 0), a.n_cen - 1); };   // never index outside the table
+  for (int t = tid; t < a.n_tok; t += 1024) atomicAdd(&cursor[clamp_id(asg[t])], 1);
+  __syncthreads();
+  // exclusive scan of the counts, 1024 at a time
+  for (int c0 = 0; c0 < a.n_cen; c0 += 1024) {
+    const int c = c0 + tid;
+    const uint32_t v = c < a.n_cen ? (uint32_t)cursor[c] : 0u;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    uint32_t ws = warp_sums[lane], winc = ws;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    const uint32_t carry = s_carry;
+    const uint32_t excl = carry + __shfl_sync(0xffffffffu, winc - ws, warp) + inc - v;
+    if (c < a.n_cen) {
+      a.count[(int64_t)problem * a.n_cen + c] = (int32_t)v;
+      a.offset[(int64_t)problem * (a.n_cen + 1) + c] = (int32_t)excl;
+      cursor[c] = (int32_t)excl;
+    }
+    const uint32_t chunk_total = __shfl_sync(0xffffffffu, winc, 31);   // every lane takes part in the shuffle
+    __syncthreads();
+    if (tid == 1023) s_carry = carry + chunk_total;
+    __syncthreads();
+  }
+  if (tid == 0) a.offset[(int64_t)problem * (a.n_cen + 1) + a.n_cen] = (int32_t)s_carry;
+  __syncthreads();
+  // stable scatter by one warp, 32 tokens at a time in token order
+  if (warp != 0) return;
+  int32_t* ord = a.order + tok0;
+  constexpr int kAhead = 8;
+  for (int t0 = 0; t0 < a.n_tok; t0 += 32 * kAhead) {
+    int32_t cl[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int t = t0 + u * 32 + lane;
+      cl[u] = t < a.n_tok ? clamp_id(asg[t]) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int t = t0 + u * 32 + lane;
+      const unsigned active = __ballot_sync(0xffffffffu, cl[u] >= 0);
+      if (cl[u] >= 0) {
+        const unsigned peers = __match_any_sync(active, cl[u]);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int pos = cursor[cl[u]] + rank;
+        ord[pos] = t;
+        __syncwarp(active);
+        if (lane == 31 - __clz(peers)) cursor[cl[u]] = pos + 1;
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// ---- update ---------------------------------------------------------------------------------
+struct UpdateArgs {
+  const uint2* centred;      // [Z, N, 128] centred keys
+  const uint2* raw_keys;     // optional: uncentred keys for the cluster-contiguous copy
+  const uint2* values;       // optional: V rows (value sums + copy)
+  const int32_t* order;
+  const int32_t* count;
+  const int32_t* offset;
+  uint2* centroids;          // [problems, n_cen, 128] in/out (centred)
+  uint2* out_centroids;      // optional final: centroid + mean
+  const uint16_t* mean;      // optional [Z, 128]
+  uint2* value_sum;          // optional [Z, C, 128]
+  uint16_t* size_dt;         // optional [Z, C]
+  uint2* keys_out;           // optional [Z, N, 128]
+  uint2* values_out;
+  int n_tok, n_cen, seg_per_group, normalize;
+  int64_t group_stride;
+};
+
+template <int DT>
+__device__ __forceinline__ void add_row(float (&acc)[4], uint2 v) {
+  acc[0] += Elem<DT>::from_bits((uint16_t)(v.x & 0xffffu));
+  acc[1] += Elem<DT>::from_bits((uint16_t)(v.x >> 16));
+  acc[2] += Elem<DT>::from_bits((uint16_t)(v.y & 0xffffu));
+  acc[3] += Elem<DT>::from_bits((uint16_t)(v.y >> 16));
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
+  const int problem = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (c >= a.n_cen) return;
+  const int z = problem / a.seg_per_group;
+  const int64_t tok0 = (int64_t)z * a.group_stride + (int64_t)(problem % a.seg_per_group) * a.n_tok;
+  const int cnt = a.count[(int64_t)problem * a.n_cen + c];
+  const int off = a.offset[(int64_t)problem * (a.n_cen + 1) + c];
+  const int32_t* ord = a.order + tok0 + off;
+  const int64_t crow = ((int64_t)problem * a.n_cen + c) * 32 + lane;    // uint2 index of this lane's 4 channels
+  if (a.size_dt) a.size_dt[(int64_t)problem * a.n_cen + c] = Elem<DT>::bits((float)cnt);
+
+  float ks[4] = {0, 0, 0, 0}, vs[4] = {0, 0, 0, 0};
+  constexpr int kUnroll = 4;
+  for (int j0 = 0; j0 < cnt; j0 += kUnroll) {
+    int rows[kUnroll];
+    uint2 kv[kUnroll], vv[kUnroll], rk[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) rows[u] = j0 + u < cnt ? ord[j0 + u] : -1;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (rows[u] >= 0) {
+        const int64_t r = (tok0 + rows[u]) * 32 + lane;
+        kv[u] = __ldg(a.centred + r);
+        if (a.values) vv[u] = __ldg(a.values + r);
+        if (a.raw_keys) rk[u] = __ldg(a.raw_keys + r);
+      }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (rows[u] >= 0) {
+        add_row<DT>(ks, kv[u]);           // sequential in list order: bit-identical to a serial sum
+        if (a.values) add_row<DT>(vs, vv[u]);
+        if (a.keys_out) {
+          const int64_t o = ((int64_t)z * a.group_stride + off + j0 + u) * 32 + lane;
+          a.keys_out[o] = rk[u];
+          a.values_out[o] = vv[u];
+        }
+      }
+  }
+  if (a.value_sum) {
+    uint2 o;
+    o.x = Elem<DT>::pack2(vs[0], vs[1]);
+    o.y = Elem<DT>::pack2(vs[2], vs[3]);
+    a.value_sum[crow] = o;
+  }
+  float x[4];
+  if (cnt > 0) {
+    const float fc = (float)cnt;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = ks[i] / fc;
+    if (a.normalize) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float nrm = sqrtf(ss);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = x[i] / nrm;
+    }
+    uint2 o;
+    o.x = Elem<DT>::pack2(x[0], x[1]);
+    o.y = Elem<DT>::pack2(x[2], x[3]);
+    a.centroids[crow] = o;
+  }
+  if (a.out_centroids) {
+    // stored centroid = round(centroid_dt + mean_dt), both already in the key dtype
+    // (cache_hub/retroinfer_cache.py:429)
+    const uint2 cd = a.centroids[crow];
+    const uint2 m = *reinterpret_cast<const uint2*>(a.mean + z * 128 + lane * 4);
+    uint2 o;
+    o.x = Elem<DT>::pack2(Elem<DT>::from_bits((uint16_t)(cd.x & 0xffffu)) + Elem<DT>::from_bits((uint16_t)(m.x & 0xffffu)),
+                          Elem<DT>::from_bits((uint16_t)(cd.x >> 16)) + Elem<DT>::from_bits((uint16_t)(m.x >> 16)));
+    o.y = Elem<DT>::pack2(Elem<DT>::from_bits((uint16_t)(cd.y & 0xffffu)) + Elem<DT>::from_bits((uint16_t)(m.y & 0xffffu)),
+                          Elem<DT>::from_bits((uint16_t)(cd.y >> 16)) + Elem<DT>::from_bits((uint16_t)(m.y >> 16)));
+    a.out_centroids[crow] = o;
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn cached = nullptr;
+  if (!cached) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    RI_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    RI_REQUIRE(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return RI_OK;
+}
+
+// rows x 128 channels, 16-bit elements, box = 128 rows x 64 channels, 128-byte swizzle
+int make_row_map(CUtensorMap* map, const void* base, int64_t rows, int dtype) {
+  EncodeTiledFn enc;
+  int rc = get_encode_fn(&enc);
+  if (rc != RI_OK) return rc;
+  const cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {256};
+  const cuuint32_t box[2] = {64, (cuuint32_t)kTileM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dtype == RI_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RI_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return RI_OK;
+}
+
+struct FitLayout {
+  int64_t cent_work, assign, order, count, offset, centred, mean, partial, error, total;
+  int chunks;
+};
+
+FitLayout fit_layout(const ri_kmeans* p, bool with_centring) {
+  FitLayout L;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = ri_align_up(off + bytes, 1024); return o; };
+  const int64_t Z = p->groups, N = p->n_tokens, C = p->n_centroids;
+  L.chunks = (int)((N + kMeanRows - 1) / kMeanRows);
+  L.error = take(4);
+  L.cent_work = take(Z * C * 256);
+  L.assign = take(Z * N * 4);
+  L.order = take(Z * N * 4);
+  L.count = take(Z * C * 4);
+  L.offset = take((Z * C + Z * (int64_t)p->n_segments) * 4 + 4);
+  L.centred = with_centring ? take(Z * N * 256) : 0;
+  L.mean = with_centring ? take(Z * 256) : 0;
+  L.partial = with_centring ? take(Z * L.chunks * 512) : 0;
+  L.total = off;
+  return L;
+}
+
+int validate_fit(const ri_kmeans* p) {
+  RI_REQUIRE(p != nullptr, "ri_kmeans is null");
+  RI_REQUIRE(p->groups > 0 && p->n_tokens > 0 && p->n_centroids > 0, "groups/n_tokens/n_centroids must be positive");
+  RI_REQUIRE(p->n_segments >= 1 && p->n_centroids % p->n_segments == 0, "n_centroids must be a multiple of n_segments");
+  RI_REQUIRE((p->n_centroids / p->n_segments) % 32 == 0,
+             "centroids per segment (%d) must be a multiple of 32", p->n_centroids / p->n_segments);
+  RI_REQUIRE(p->n_centroids <= 49152, "n_centroids=%d too large (limit 49152)", p->n_centroids);
+  RI_REQUIRE(p->n_iters >= 1, "n_iters must be at least 1");
+  RI_REQUIRE(p->dtype == RI_BF16 || p->dtype == RI_F16, "dtype=%d unsupported", p->dtype);
+  RI_REQUIRE((int64_t)p->groups * p->n_tokens < (1ll << 31), "groups*n_tokens must stay below 2^31 rows");
+  RI_REQUIRE(p->n_tokens / p->n_segments >= 1, "fewer tokens than segments");
+  return RI_OK;
+}
+
+// With RI_KMEANS_TRACE=1 in the environment every launch is followed by a stream synchronise and a
+// line on stderr (debugging aid; never set it while capturing a graph).
+int trace_stage(const char* name, cudaStream_t s) {
+  static const bool on = getenv("RI_KMEANS_TRACE") != nullptr;
+  if (!on) return RI_OK;
+  const cudaError_t e = cudaStreamSynchronize(s);
+  fprintf(stderr, "[ri_kmeans] %s: %s\n", name, cudaGetErrorString(e));
+  fflush(stderr);
+  if (e != cudaSuccess) return ri_fail(RI_ERR_CUDA, "%s failed: %s", name, cudaGetErrorString(e));
+  return RI_OK;
+}
+
+template <int DT>
+int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStream_t s) {
+  uint8_t* sc = static_cast<uint8_t*>(p->d_scratch);
+  const int Z = p->groups, N = p->n_tokens, C = p->n_centroids, S = p->n_segments;
+  int* err = reinterpret_cast<int*>(sc + L.error);
+  void* cent = sc + L.cent_work;
+  int32_t* assign = p->d_assign ? p->d_assign : reinterpret_cast<int32_t*>(sc + L.assign);
+  int32_t* order = p->d_order ? p->d_order : reinterpret_cast<int32_t*>(sc + L.order);
+  int32_t* count_work = reinterpret_cast<int32_t*>(sc + L.count);
+  int32_t* offset_work = reinterpret_cast<int32_t*>(sc + L.offset);
+
+  RI_CUDA_OK(cudaMemsetAsync(err, 0, 4, s));
+  int rc0 = RI_OK;
+  {
+    const float step = (float)((double)N / (double)C);
+    const float half = (float)((double)N / (double)C / 2.0);
+    dim3 grid((C * 16 + 255) / 256, Z);
+    init_centroids_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(centred), static_cast<uint4*>(cent), N, C, step, half);
+    RI_LAUNCH_OK("init_centroids_kernel");
+    if ((rc0 = trace_stage("init_centroids", s)) != RI_OK) return rc0;
+  }
+  CUtensorMap map_keys, map_cent;
+  int rc = make_row_map(&map_keys, centred, (int64_t)Z * N, DT);
+  if (rc != RI_OK) return rc;
+  rc = make_row_map(&map_cent, cent, (int64_t)Z * C, DT);
+  if (rc != RI_OK) return rc;
+  RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAssignSmem));
+
+  for (int it = 0; it < p->n_iters; ++it) {
+    const bool last = it == p->n_iters - 1;
+    const int seg = last ? 1 : S;
+    const int n_tok = last ? N : N / S;
+    const int n_cen = C / seg;
+    const int problems = Z * seg;
+    AssignArgs aa;
+    aa.assign = assign; aa.error_flag = err; aa.n_tok = n_tok; aa.n_cen = n_cen; aa.seg_per_group = seg;
+    aa.group_stride = N;
+    aa.idesc = (1u << 4) | ((DT == RI_BF16 ? 1u : 0u) << 7) | ((DT == RI_BF16 ? 1u : 0u) << 10) |
+               ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    dim3 agrid((n_tok + kTileM - 1) / kTileM, problems);
+    kmeans_assign_kernel<<<agrid, kAssignThreads, kAssignSmem, s>>>(map_keys, map_cent, aa);
+    RI_LAUNCH_OK("kmeans_assign_kernel");
+    if ((rc0 = trace_stage("assign", s)) != RI_OK) return rc0;
+
+    BucketArgs ba;
+    ba.assign = assign; ba.order = order;
+    ba.count = last && p->d_cluster_count ? p->d_cluster_count : count_work;
+    ba.offset = last && p->d_cluster_offset ? p->d_cluster_offset : offset_work;
+    ba.n_tok = n_tok; ba.n_cen = n_cen; ba.seg_per_group = seg; ba.group_stride = N;
+    const size_t bsmem = (size_t)n_cen * 4;
+    if (bsmem > 48 * 1024)
+      RI_CUDA_OK(cudaFuncSetAttribute(kmeans_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
+    kmeans_bucket_kernel<<<problems, 1024, bsmem, s>>>(ba);
+    RI_LAUNCH_OK("kmeans_bucket_kernel");
+    if ((rc0 = trace_stage("bucket", s)) != RI_OK) return rc0;
+
+    UpdateArgs ua = {};
+    ua.centred = static_cast<const uint2*>(centred);
+    ua.order = order; ua.count = ba.count; ua.offset = ba.offset;
+    ua.centroids = static_cast<uint2*>(cent);
+    ua.n_tok = n_tok; ua.n_cen = n_cen; ua.seg_per_group = seg; ua.normalize = last ? 0 : 1; ua.group_stride = N;
+    if (last) {
+      ua.values = static_cast<const uint2*>(p->d_values);
+      ua.value_sum = static_cast<uint2*>(p->d_value_sum);
+      ua.size_dt = static_cast<uint16_t*>(p->d_cluster_size);
+      if (p->d_keys_out) {
+        ua.raw_keys = static_cast<const uint2*>(p->d_keys);
+        ua.keys_out = static_cast<uint2*>(p->d_keys_out);
+        ua.values_out = static_cast<uint2*>(p->d_values_out);
+      }
+      if (p->center) {
+        ua.mean = reinterpret_cast<const uint16_t*>(sc + L.mean);
+        ua.out_centroids = static_cast<uint2*>(p->d_centroids);
+      }
+    }
+    dim3 ugrid((n_cen + 7) / 8, problems);
+    kmeans_update_kernel<DT><<<ugrid, 256, 0, s>>>(ua);
+    RI_LAUNCH_OK("kmeans_update_kernel");
+    if ((rc0 = trace_stage("update", s)) != RI_OK) return rc0;
+  }
+  if (!p->center)
+    RI_CUDA_OK(cudaMemcpyAsync(p->d_centroids, cent, (size_t)Z * C * 256, cudaMemcpyDeviceToDevice, s));
+  if (p->d_error) RI_CUDA_OK(cudaMemcpyAsync(p->d_error, err, 4, cudaMemcpyDeviceToDevice, s));
+  return RI_OK;
+}
+
+template <int DT>
+int run_build(const ri_kmeans* p, cudaStream_t s) {
+  const FitLayout L = fit_layout(p, p->center != 0);
+  uint8_t* sc = static_cast<uint8_t*>(p->d_scratch);
+  const void* centred = p->d_keys;
+  if (p->center) {
+    const int Z = p->groups, N = p->n_tokens;
+    float* partial = reinterpret_cast<float*>(sc + L.partial);
+    uint16_t* mean = reinterpret_cast<uint16_t*>(sc + L.mean);
+    colsum_partial_kernel<DT><<<dim3(L.chunks, Z), 256, 0, s>>>(static_cast<const uint4*>(p->d_keys), partial, N, L.chunks);
+    RI_LAUNCH_OK("colsum_partial_kernel");
+    colmean_final_kernel<DT><<<Z, 128, 0, s>>>(partial, mean, N, L.chunks);
+    RI_LAUNCH_OK("colmean_final_kernel");
+    const int64_t pieces = (int64_t)N * 16;
+    centre_apply_kernel<DT><<<dim3((unsigned)((pieces + 255) / 256), Z), 256, 0, s>>>(
+        static_cast<const uint4*>(p->d_keys), mean, reinterpret_cast<uint4*>(sc + L.centred), pieces);
+    RI_LAUNCH_OK("centre_apply_kernel");
+    centred = sc + L.centred;
+    if (p->d_mean_key) RI_CUDA_OK(cudaMemcpyAsync(p->d_mean_key, mean, (size_t)Z * 256, cudaMemcpyDeviceToDevice, s));
+  }
+  return run_fit<DT>(p, L, centred, s);
+}
+
+}  // namespace
+
+extern "C" int64_t ri_kmeans_scratch_bytes(const ri_kmeans* p) {
+  if (validate_fit(p) != RI_OK) return RI_ERR_INVALID;
+  return fit_layout(p, p->center != 0).total;
+}
+
+extern "C" int ri_kmeans_build(const ri_kmeans* p, void* stream) {
+  int rc = validate_fit(p);
+  if (rc != RI_OK) return rc;
+  RI_REQUIRE(p->d_keys && p->d_values && p->d_centroids && p->d_value_sum && p->d_cluster_size && p->d_scratch,
+             "ri_kmeans: a required pointer is null");
+  RI_REQUIRE((p->d_keys_out == nullptr) == (p->d_values_out == nullptr), "keys_out and values_out go together");
+  RI_REQUIRE(((uintptr_t)p->d_keys | (uintptr_t)p->d_values | (uintptr_t)p->d_centroids | (uintptr_t)p->d_value_sum |
+              (uintptr_t)p->d_scratch | (uintptr_t)p->d_keys_out | (uintptr_t)p->d_values_out) % 16 == 0,
+             "tensor pointers must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return p->dtype == RI_BF16 ? run_build<RI_BF16>(p, s) : run_build<RI_F16>(p, s);
+}
