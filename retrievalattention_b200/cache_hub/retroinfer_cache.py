@@ -1,0 +1,179 @@
+"""``retroinfer_cache`` with the reference's interface (cache_hub/retroinfer_cache.py:16-697), backed
+by the CUDA kernels of this package and with the whole cluster-contiguous KV resident in HBM.
+
+What is the same: constructor arguments, ``prefill_update_kv_cache`` / ``sync`` / ``prepare_cache`` /
+``decode_update_kv_cache`` / ``compute`` and their return values, the attributes callers read
+(``context``, ``layer_num``), the steady-zone bookkeeping (``static_pattern_total``), the index
+parameters and the page budget ``buffer_size`` (:107-111).
+
+What differs underneath: the index is built on the GPU by ``ri_kmeans_build`` (no pinned-host
+offload, no CPU re-layout), and one decode layer is one ``ri_wave_decode_layer`` call with no host
+synchronisation.  ``core``, ``cache_cluster_num`` and ``use_cluster_estimation`` are accepted for
+compatibility; the GPU page cache they size does not exist here because nothing lives on the host.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import wave
+from .cache import KV_Cache
+from .kmeans import build_index
+
+THRESHOLD_LENGTH = 1024   # reference: re-index period in generated tokens (:13)
+
+
+class retroinfer_cache(KV_Cache):
+    def __init__(self, valid_start, layer_num: int, batch_size: int, max_length: int, num_key_value_heads: int,
+                 num_heads: int, head_dim: int, dtype: torch.dtype, layer_mapping: dict, max_new_length: int,
+                 static_pattern_start: int, static_pattern_end: int, core: int, n_centroids: int, n_segment: int,
+                 nprobe: int, max_compute_cluster_num: int, cache_unit_size: int, cache_cluster_num: int,
+                 num_gpus: int, model_size: int, use_cluster_estimation: bool = False) -> None:
+        super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
+                         layer_mapping, num_gpus, model_size)
+        if head_dim != 128:
+            raise ValueError("the wave-index kernels are built for head_dim 128 (as the reference's copy kernels are)")
+        self.valid_start = valid_start
+        self.static_pattern_start = static_pattern_start
+        self.static_pattern_end = static_pattern_end
+        self.static_pattern_total = static_pattern_start + static_pattern_end
+        self.group_size = num_heads // num_key_value_heads
+        self.batch_groups = batch_size * num_key_value_heads
+        self.page_size = cache_unit_size
+        self.core = core
+        self.use_cluster_estimation = use_cluster_estimation
+
+        self.input_length = max_length - max_new_length
+        self.max_new_length = min(max_new_length - 1, THRESHOLD_LENGTH)       # :64
+        self.static_stride = self.static_pattern_total + self.max_new_length
+        self.n_centroids = n_centroids
+        self.n_segment = n_segment
+        self.nprobe = nprobe
+        self.max_compute_cluster_num = max_compute_cluster_num
+        self.es_cluster_num = max_compute_cluster_num - nprobe
+        avg_cluster_size = (self.input_length - self.static_pattern_total) // n_centroids
+        pages_per_cluster = math.ceil(avg_cluster_size / self.page_size)
+        self.cache_size = cache_cluster_num * pages_per_cluster
+        self.buffer_size = max(int(nprobe * 4), 16) * pages_per_cluster      # :111, page budget per group
+        self.list_stride = self.input_length - self.static_pattern_total
+
+        g, c, d = self.batch_groups, n_centroids, head_dim
+        self.steady_zone_keys, self.steady_zone_values = [], []
+        self.centroids, self.value_sum, self.cluster_size = [], [], []
+        self.cluster_count, self.cluster_offset, self.centroids_mask = [], [], []
+        self.list_keys, self.list_values = [], []
+        self._error_flags = []
+        for ldx in range(layer_num):
+            dev = layer_mapping[str(ldx)]
+            z = lambda *shape, dt=dtype: torch.zeros(shape, dtype=dt, device=dev)  # noqa: E731
+            self.steady_zone_keys.append(z(batch_size, self.kv_head, self.static_stride, d))
+            self.steady_zone_values.append(z(batch_size, self.kv_head, self.static_stride, d))
+            self.centroids.append(z(g, c, d))
+            self.value_sum.append(z(g, c, d))
+            self.cluster_size.append(z(g, c))
+            self.cluster_count.append(z(g, c, dt=torch.int32))
+            self.cluster_offset.append(z(g, c + 1, dt=torch.int32))
+            self.centroids_mask.append(z(g, c, dt=torch.bool))
+            self.list_keys.append(z(batch_size, self.kv_head, self.list_stride, d))
+            self.list_values.append(z(batch_size, self.kv_head, self.list_stride, d))
+
+        self.shape = wave.WaveShape(g, self.group_size, c, nprobe, self.es_cluster_num, self.page_size,
+                                    self.buffer_size, self.list_stride, self.static_stride, dtype)
+        # per device: scratch shared by the layers of that device, and the device-side counters
+        self._per_device = {}
+        for dev in sorted(set(layer_mapping.values())):
+            self._per_device[dev] = {
+                "scratch": wave.new_scratch(self.shape, dev),
+                "static_len": torch.tensor([self.static_pattern_total + 1], dtype=torch.int32, device=dev),
+                "append_pos": torch.tensor([self.static_pattern_total], dtype=torch.int32, device=dev),
+            }
+        self._layers = [None] * layer_num
+
+    # ------------------------------------------------------------------ prefill
+    def prefill_update_kv_cache(self, query_states, key_states, value_states, layer_idx, batch_idx):
+        """One request, one layer (:368-441).  key/value_states: [1, seq_len, kv_heads, head_dim]."""
+        bsz, seq_len, group_num, head_dim = key_states.shape
+        assert bsz == 1, "Multi-batch prefilling only support prefill single batch one by one."
+        assert seq_len <= self.input_length, f"seq_len({seq_len}) should less than input_length({self.input_length})"
+        vs = int(self.valid_start[batch_idx])
+        start, end, total = self.static_pattern_start, self.static_pattern_end, self.static_pattern_start + self.static_pattern_end
+        valid_length = seq_len - total - vs
+
+        temp_keys = key_states[0, vs + start:seq_len - end].transpose(0, 1).contiguous()      # [kv_heads, N_b, d]
+        temp_values = value_states[0, vs + start:seq_len - end].transpose(0, 1).contiguous()
+
+        sk, sv = self.steady_zone_keys[layer_idx], self.steady_zone_values[layer_idx]
+        sk[batch_idx, :, :start] = key_states[0, vs:vs + start].transpose(0, 1)
+        sk[batch_idx, :, start:total] = key_states[0, seq_len - end:seq_len].transpose(0, 1)
+        sv[batch_idx, :, :start] = value_states[0, vs:vs + start].transpose(0, 1)
+        sv[batch_idx, :, start:total] = value_states[0, seq_len - end:seq_len].transpose(0, 1)
+
+        r = build_index(temp_keys, temp_values, self.n_centroids, self.n_segment)
+        rows = slice(batch_idx * self.kv_head, (batch_idx + 1) * self.kv_head)
+        self.centroids[layer_idx][rows].copy_(r["centroids"])
+        self.value_sum[layer_idx][rows].copy_(r["value_sum"])
+        self.cluster_size[layer_idx][rows].copy_(r["cluster_size"])
+        self.cluster_count[layer_idx][rows].copy_(r["cluster_count"])
+        self.cluster_offset[layer_idx][rows].copy_(r["cluster_offset"])
+        self.centroids_mask[layer_idx][rows].copy_(r["cluster_count"] == 0)
+        self.list_keys[layer_idx][batch_idx, :, :valid_length].copy_(r["keys"])
+        self.list_values[layer_idx][batch_idx, :, :valid_length].copy_(r["values"])
+        self._error_flags.append(r["error"])
+
+        if layer_idx == self.layer_num - 1 and batch_idx + bsz == self.batch_size:
+            self.context += seq_len
+        return key_states[:, vs:], value_states[:, vs:]
+
+    def sync(self, layer_idx, batch_idx):
+        """The reference waits here for its host offload and starts the CPU re-layout (:443-458);
+        the layout was already written by the clustering pass, so there is nothing to wait for."""
+        return None
+
+    def prepare_cache(self):
+        """Finish prefill (:336-365): check the clustering status words and bind every layer."""
+        torch.cuda.synchronize()
+        for flag in self._error_flags:
+            if int(flag.item()) != 0:
+                raise RuntimeError(f"clustering gave up on a device-side wait (code {int(flag.item())})")
+        self._error_flags.clear()
+        g = self.batch_groups
+        for ldx in range(self.layer_num):
+            per = self._per_device[self.layer_mapping[str(ldx)]]
+            self._layers[ldx] = wave.WaveIndexLayer(
+                self.shape, centroids=self.centroids[ldx], value_sum=self.value_sum[ldx],
+                cluster_size=self.cluster_size[ldx], cluster_count=self.cluster_count[ldx],
+                cluster_offset=self.cluster_offset[ldx],
+                keys=self.list_keys[ldx].view(g, self.list_stride, self.head_dim),
+                values=self.list_values[ldx].view(g, self.list_stride, self.head_dim),
+                steady_keys=self.steady_zone_keys[ldx].view(g, self.static_stride, self.head_dim),
+                steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
+                static_len=per["static_len"], scratch=per["scratch"])
+
+    # ------------------------------------------------------------------ decode
+    def decode_update_kv_cache(self, key_states, value_states, layer_idx):
+        """Append the new token's K/V ([bs, 1, kv_heads, d]) to the steady zone (:527-546)."""
+        if self.static_pattern_total == self.static_pattern_start + self.static_pattern_end + THRESHOLD_LENGTH:
+            raise NotImplementedError(
+                "re-indexing after 1024 generated tokens (reference _update_kv_cache, :462-524) is not built yet")
+        per = self._per_device[self.layer_mapping[str(layer_idx)]]
+        g = self.batch_groups
+        wave.steady_append(key_states.contiguous(), value_states.contiguous(),
+                           self.steady_zone_keys[layer_idx].view(g, self.static_stride, self.head_dim),
+                           self.steady_zone_values[layer_idx].view(g, self.static_stride, self.head_dim),
+                           per["append_pos"])
+        if layer_idx == self.layer_num - 1:
+            self.context += 1
+            self.static_pattern_total += 1
+            for p in self._per_device.values():
+                p["append_pos"].add_(1)
+        return None, None
+
+    def compute(self, queries, layer_idx, queries_next=None):
+        """Wave-index attention for one layer (:549-697).  queries: [batch, 1, heads, d]."""
+        out = self._layers[layer_idx].compute(queries.contiguous())
+        if layer_idx == self.layer_num - 1:
+            # every layer of a step attends static_pattern_total(+1) rows (:559); advance for the next step
+            for p in self._per_device.values():
+                p["static_len"].add_(1)
+        return out.view(self.batch_size, 1, self.num_heads, self.head_dim)
