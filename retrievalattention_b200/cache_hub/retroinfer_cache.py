@@ -169,9 +169,10 @@ class retroinfer_cache(KV_Cache):
                 p["append_pos"].add_(1)
         return None, None
 
-    def compute(self, queries, layer_idx, queries_next=None):
-        """Wave-index attention for one layer (:549-697).  queries: [batch, 1, heads, d]."""
-        out = self._layers[layer_idx].compute(queries.contiguous())
+    def compute(self, queries, layer_idx, queries_next=None, out=None):
+        """Wave-index attention for one layer (:549-697).  queries: [batch, 1, heads, d].
+        ``out`` (optional, not in the reference) receives the result instead of a new tensor."""
+        out = self._layers[layer_idx].compute(queries.contiguous(), out)
         if layer_idx == self.layer_num - 1:
             # every layer of a step attends static_pattern_total(+1) rows (:559); advance for the next step
             for p in self._per_device.values():
