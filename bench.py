@@ -48,9 +48,17 @@ METRIC = "decode tok/s at 128K ctx (Llama-3-8B geometry); attn kernel HBM GB/s v
 class Workload:
     """One rank's resident state: the cache of every layer and the per-step inputs."""
 
-    def __init__(self, geo, device, total_steps, kmeans_iters=10, rank=0, log=None):
+    def __init__(self, geo, device, total_steps, kmeans_iters=10, rank=0, log=None, world=1):
         from retrievalattention_b200.cache_hub import retroinfer_cache
+        from retrievalattention_b200.head_shard import HeadGather, HeadShard
 
+        # N ranks: global batch = batch * N requests, KV heads sharded over the ranks (then batch), so
+        # every rank holds the same number of (request, kv-head) groups as the 1-GPU workload.
+        self.global_geo = geo
+        self.shard = HeadShard(rank, world, geo.kv_heads, geo.q_heads, geo.batch * world)
+        geo = replace(geo, kv_heads=self.shard.local_kv_heads, q_heads=self.shard.local_q_heads,
+                      batch=self.shard.local_batch)
+        self.gather = HeadGather(self.shard, HeadGather.make_groups(self.shard)) if world > 1 else None
         self.geo, self.device = geo, device
         self.cfg = cfg = geo.index()
         max_new = total_steps + 2
@@ -89,6 +97,10 @@ class Workload:
         self.k_in = torch.zeros(shp_kv[1:], dtype=torch.bfloat16, device=device)
         self.v_in = torch.zeros(shp_kv[1:], dtype=torch.bfloat16, device=device)
         self.out = torch.zeros(shp_q[1:], dtype=torch.bfloat16, device=device)
+        self.gathered = None
+        if self.gather is not None:
+            self.gathered = torch.zeros((geo.layers, self.shard.head_shards) + tuple(shp_q[2:]), dtype=torch.bfloat16,
+                                        device=device)
         self.graph = None
 
     def step_body(self):
@@ -98,12 +110,28 @@ class Workload:
         for l in range(self.geo.layers):
             self.cache.decode_update_kv_cache(self.k_in[l], self.v_in[l], l)
             self.cache.compute(self.q_in[l], l, out=self.out[l])
+            if self.gather is not None:      # head slices of all ranks -> [B, 1, Hq, d] for o_proj
+                self.gather(self.out[l], self.gathered[l])
 
     def capture(self):
         self.step_body()                     # one eager step first (also advances the steady zone)
         torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.step_body()
+            self.graph = graph
+        except Exception as exc:             # e.g. a collective that cannot be captured: step eagerly
+            if self.gather is None:
+                raise
+            self.graph = None
+            self.capture_error = repr(exc)[:200]
+            torch.cuda.synchronize()
+
+    def replay(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
             self.step_body()
 
     def launches_per_step(self):
@@ -234,7 +262,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
     warm = max(args.warmup, 3)
     stage_steps = min(args.steps, 4)
     total = 2 * (warm + args.steps) + stage_steps + 2
-    wl = Workload(geo, device, total, args.kmeans_iters, rank, log)
+    wl = Workload(geo, device, total, args.kmeans_iters, rank, log, world)
     wl.capture()      # consumes 2 steps of the steady zone
 
     def barrier():
@@ -246,7 +274,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
     def run_resident(first, count):
         for st in range(first, first + count):
             wl.q_in.copy_(wl.q_all[st]); wl.k_in.copy_(wl.k_all[st]); wl.v_in.copy_(wl.v_all[st])
-            wl.graph.replay()
+            wl.replay()
 
     # ---- `value`: inputs resident in HBM, one graph replay per step ----
     run_resident(0, warm)
@@ -272,7 +300,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
             wl.q_in.copy_(q_host[st], non_blocking=True)
             wl.k_in.copy_(k_host[st], non_blocking=True)
             wl.v_in.copy_(v_host[st], non_blocking=True)
-            wl.graph.replay()
+            wl.replay()
             out_host.copy_(wl.out, non_blocking=True)
             torch.cuda.current_stream().synchronize()    # the caller consumes this step's output
 
@@ -292,6 +320,8 @@ def run_decode(geo, args, rank, world, local_rank, log):
     # ---- per-kernel time and roofline (separate eager pass, events around each launch) ----
     stage_ms, n_ret_rows, static_len = time_stages(wl, 2 * (warm + args.steps), stage_steps)
     if rank != 0:
+        dist.barrier()                 # rank 0 is still timing the CPU baseline
+        dist.destroy_process_group()
         return
     peak, _, peak_kind = measured_peaks()
     alg = algorithmic_bytes(wl, n_ret_rows, static_len)
@@ -301,22 +331,28 @@ def run_decode(geo, args, rank, world, local_rank, log):
     step_alg = sum(alg.values()) * geo.layers
     tokens = geo.batch * world * args.steps
     cfg = wl.cfg
+    lg = wl.geo
     result = {
         "metric": METRIC, "value": round(tokens / (ms / 1e3), 2), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": warm, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{geo.name}: wave-index decode attention hot path through retroinfer_cache "
                                f"(decode_update_kv_cache + compute), {geo.layers} layers, {geo.q_heads}q/{geo.kv_heads}kv "
-                               f"heads, d128, batch {geo.batch}/GPU, ctx {geo.context}, {cfg.n_centroids} centroids, "
-                               f"{cfg.n_segment} segments, nprobe {cfg.nprobe}, estimate {wl.shape.n_estimate}",
+                               f"heads, d128, global batch {geo.batch * world}, ctx {geo.context}, {cfg.n_centroids} "
+                               f"centroids, {cfg.n_segment} segments, nprobe {cfg.nprobe}, estimate {wl.shape.n_estimate}",
+                   "parallelism": (f"{world} ranks: {wl.shard.head_shards} KV-head shards x {wl.shard.batch_shards} batch "
+                                   f"shards; per rank {lg.kv_heads} kv heads x batch {lg.batch} = {wl.shape.groups} groups; "
+                                   f"one NCCL all-gather of the head slices per layer") if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (each layer-step touches its own ~110 MB; ~3.5 GB per step)",
                    "index": f"built by ri_kmeans_build during untimed set-up ({args.kmeans_iters} iterations, "
                             f"median {wl.prefill_index_ms:.1f} ms per request-layer incl. layout)",
-                   "graph": "one CUDA graph per decode step"},
+                   "graph": "one CUDA graph per decode step" if wl.graph is not None else
+                            "eager stepping (capture failed: " + getattr(wl, "capture_error", "?") + ")"},
         "e2e": {"value": round(tokens / (ms_e2e / 1e3), 2), "unit": "tok/s",
                 "h2d_bytes_per_step": int(2 * (wl.q_in.numel() + wl.k_in.numel() + wl.v_in.numel())),
                 "d2h_bytes_per_step": int(2 * wl.out.numel())},
         "gpu_launches": wl.launches_per_step() * args.steps,
+        "nccl_collectives": (geo.layers * args.steps) if world > 1 else 0,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "wave_" + top + "_kernel", "achieved": kernels[top]["gbs"], "peak": peak,
                      "unit": "GB/s", "frac": kernels[top]["frac"], "peak_kind": "of " + peak_kind, "traffic": None,
@@ -331,6 +367,9 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                   "sample": f"layer 0 of the same workload, all {geo.groups} groups, median of 2 runs "
                                             f"({sec * 1e3:.1f} ms), scaled by {geo.layers} layers"}
     print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def reference_arm(geo, args, log):

@@ -165,6 +165,39 @@ typedef struct ri_kmeans {
 int64_t ri_kmeans_scratch_bytes(const ri_kmeans* p);
 int ri_kmeans_build(const ri_kmeans* p, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Host-side wave buffer for the host tier (clusters whose KV stays in pinned host memory and is
+ * cached page-wise on the GPU).  Replaces the descriptor/LRU part of `WaveBufferCPU`
+ * (library/retroinfer/retroinfer_kernels/src/wave_buffer_cpu.cpp:261-816 and its pybind
+ * interface :822-849): `set_indices` :442-486, the `parse_clusters` step of
+ * `async_construction` :513-542/:592-616, the descriptor step of `update_kv` :646-684,
+ * `batch_access` (`para_batch_access`) :789-809 and `sync` :811-814.  The KV re-layout
+ * (`organize_kv` :545-567) is not here: ri_kmeans_build writes it on the GPU.
+ *
+ * All index arrays are host memory owned by the caller (the reference pins them so that kernels
+ * read them through UVA), laid out [groups, buffer_size] / [groups] exactly as in
+ * cache_hub/retroinfer_cache.py:124-185.  Page ids are handed out lowest-free-first.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ri_wave_buffer ri_wave_buffer;
+
+ri_wave_buffer* ri_wb_create(int32_t batch_size, int32_t group_num, int32_t nprobe, int32_t block_size,
+                             int32_t n_centroids, int32_t final_n_centroids, int32_t buffer_size,
+                             int32_t capacity, int32_t threads);   /* NULL on bad arguments */
+void ri_wb_destroy(ri_wave_buffer* wb);
+int ri_wb_set_indices(ri_wave_buffer* wb, int32_t* hit_ids, int32_t* hit_sizes, int32_t* hit_cumsum,
+                      int32_t* hit_nums, int32_t* miss_ids, int32_t* miss_sizes, int32_t* miss_cumsum,
+                      int32_t* miss_nums, int32_t* update_buffer_indices, int32_t* update_sizes,
+                      int32_t* update_cache_indices, int32_t* update_nums, const int64_t* searched_clusters);
+/* cluster sizes of one request: [group_num, n_centroids]; resets that request's page cache */
+int ri_wb_set_clusters(ri_wave_buffer* wb, int32_t batch_idx, const int32_t* cluster_sizes);
+/* clusters added by a re-index during decoding: [batch*group_num, n_new] */
+int ri_wb_append_clusters(ri_wave_buffer* wb, const int32_t* cluster_sizes, int32_t n_new);
+/* Blocks until the hit/miss lists are written, then starts the LRU update in the background.
+ * Returns the number of groups whose retrieval was cut by the page budget (>= 0) or an error. */
+int ri_wb_batch_access(ri_wave_buffer* wb);
+int ri_wb_sync(ri_wave_buffer* wb);          /* waits for the background update (update lists valid) */
+int64_t ri_wb_rows_used(const ri_wave_buffer* wb, int32_t group);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,6 +71,22 @@ def _load() -> C.CDLL:
     lib.ri_kmeans_scratch_bytes.argtypes = [C.POINTER(KMeans)]
     lib.ri_kmeans_build.restype = C.c_int
     lib.ri_kmeans_build.argtypes = [C.POINTER(KMeans), C.c_void_p]
+    lib.ri_wb_create.restype = C.c_void_p
+    lib.ri_wb_create.argtypes = [C.c_int32] * 9
+    lib.ri_wb_destroy.restype = None
+    lib.ri_wb_destroy.argtypes = [C.c_void_p]
+    lib.ri_wb_set_indices.restype = C.c_int
+    lib.ri_wb_set_indices.argtypes = [C.c_void_p] * 14
+    lib.ri_wb_set_clusters.restype = C.c_int
+    lib.ri_wb_set_clusters.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
+    lib.ri_wb_append_clusters.restype = C.c_int
+    lib.ri_wb_append_clusters.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
+    lib.ri_wb_batch_access.restype = C.c_int
+    lib.ri_wb_batch_access.argtypes = [C.c_void_p]
+    lib.ri_wb_sync.restype = C.c_int
+    lib.ri_wb_sync.argtypes = [C.c_void_p]
+    lib.ri_wb_rows_used.restype = C.c_int64
+    lib.ri_wb_rows_used.argtypes = [C.c_void_p, C.c_int32]
     lib.ri_steady_append.restype = C.c_int
     lib.ri_steady_append.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_int32, C.c_void_p]
     return lib

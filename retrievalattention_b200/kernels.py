@@ -1,0 +1,81 @@
+"""The operator surface of the reference's ``retroinfer_kernels`` package
+(library/retroinfer/retroinfer_kernels/__init__.py:1-3), bound to ``libri_b200.so``.
+
+``ThreadPool`` / ``WaveBufferCPU`` keep the constructor and method names of the pybind classes
+(wave_buffer_cpu.cpp:822-849).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+class ThreadPool:
+    """Placeholder with the reference's interface (``ThreadPool(n).get()``, wave_buffer_cpu.cpp:17-35).
+    Each ``WaveBufferCPU`` here owns its workers, so the handle only carries the thread count."""
+
+    def __init__(self, num_threads: int):
+        self.num_threads = int(num_threads)
+
+    def get(self):
+        return self
+
+
+class WaveBufferCPU:
+    """Host-side LRU page cache of one layer (wave_buffer_cpu.cpp:261-816)."""
+
+    def __init__(self, batch_size, group_num, dim, nprobe, block_size, n_centroids, final_n_centroids, buffer_size,
+                 capacity, threads, pool=None):
+        if dim != 128:
+            raise ValueError("head_dim must be 128")
+        self.batch_size, self.group_num, self.n_centroids = batch_size, group_num, n_centroids
+        self._h = _lib.lib.ri_wb_create(batch_size, group_num, nprobe, block_size, n_centroids, final_n_centroids,
+                                        buffer_size, capacity, threads)
+        if not self._h:
+            raise ValueError(_lib.lib.ri_last_error().decode())
+        self._keep = []
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            _lib.lib.ri_wb_destroy(h)
+
+    def set_indices(self, hit_block_ids, hit_block_sizes, hit_block_sizes_cumsum, hit_block_nums, miss_block_ids,
+                    miss_block_sizes, miss_block_sizes_cumsum, miss_block_nums, update_buffer_indices,
+                    update_block_sizes, update_cache_indices, update_block_nums, searched_clusters):
+        ts = [hit_block_ids, hit_block_sizes, hit_block_sizes_cumsum, hit_block_nums, miss_block_ids, miss_block_sizes,
+              miss_block_sizes_cumsum, miss_block_nums, update_buffer_indices, update_block_sizes, update_cache_indices,
+              update_block_nums]
+        for t in ts:
+            assert t.dtype == torch.int32 and t.device.type == "cpu" and t.is_contiguous()
+        assert searched_clusters.dtype == torch.int64 and searched_clusters.device.type == "cpu"
+        self._keep = ts + [searched_clusters]          # the library keeps raw pointers (as the reference does)
+        _lib.check(_lib.lib.ri_wb_set_indices(self._h, *[t.data_ptr() for t in self._keep]), "ri_wb_set_indices")
+
+    def set_kv(self, ivf_key, ivf_value, input_keys, input_values):
+        """Accepted for compatibility: the cluster-contiguous copy is produced on the GPU by the
+        clustering pass, not by host memcpy (wave_buffer_cpu.cpp:488-507, :545-567)."""
+        return None
+
+    def async_construction(self, clusters, cluster_size, batch_idx):
+        """Register one request's cluster sizes ([group_num, n_centroids] int32); the inverted lists
+        are not needed on the host (wave_buffer_cpu.cpp:592-616)."""
+        cs = cluster_size.to(torch.int32).cpu().contiguous()
+        _lib.check(_lib.lib.ri_wb_set_clusters(self._h, int(batch_idx), cs.data_ptr()), "ri_wb_set_clusters")
+
+    def construction_sync(self):
+        return None
+
+    def update_kv(self, update_keys, update_values, clusters, cluster_size):
+        cs = cluster_size.to(torch.int32).cpu().contiguous()
+        _lib.check(_lib.lib.ri_wb_append_clusters(self._h, cs.data_ptr(), cs.shape[1]), "ri_wb_append_clusters")
+
+    def batch_access(self) -> int:
+        rc = _lib.lib.ri_wb_batch_access(self._h)
+        if rc < 0:
+            _lib.check(rc, "ri_wb_batch_access")
+        return rc
+
+    def sync(self):
+        _lib.check(_lib.lib.ri_wb_sync(self._h), "ri_wb_sync")
