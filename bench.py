@@ -256,8 +256,13 @@ def run_decode(geo, args, rank, world, local_rank, log):
     device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN"):
+            os.environ["NCCL_DEBUG"] = "ERROR"     # keep NCCL's banner off stdout: one JSON line only
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
+        # Host-side barriers and the max-over-ranks reduction go over gloo: an eager NCCL collective
+        # issued after graph-captured ones on the same communicator did not return on this pool.
+        cpu_group = dist.new_group(backend="gloo")
 
     warm = max(args.warmup, 3)
     stage_steps = min(args.steps, 4)
@@ -268,8 +273,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+            dist.barrier(group=cpu_group)
 
     def run_resident(first, count):
         for st in range(first, first + count):
@@ -313,15 +317,14 @@ def run_decode(geo, args, rank, world, local_rank, log):
     ms_e2e = e0.elapsed_time(e1)
 
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = torch.tensor([ms, ms_e2e])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=cpu_group)
         ms, ms_e2e = t.tolist()
 
     # ---- per-kernel time and roofline (separate eager pass, events around each launch) ----
     stage_ms, n_ret_rows, static_len = time_stages(wl, 2 * (warm + args.steps), stage_steps)
     if rank != 0:
-        dist.barrier()                 # rank 0 is still timing the CPU baseline
-        dist.destroy_process_group()
+        dist.barrier(group=cpu_group)  # rank 0 is still timing the CPU baseline
         return
     peak, _, peak_kind = measured_peaks()
     alg = algorithmic_bytes(wl, n_ret_rows, static_len)
@@ -368,8 +371,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                             f"({sec * 1e3:.1f} ms), scaled by {geo.layers} layers"}
     print(json.dumps(result), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        dist.barrier(group=cpu_group)
 
 
 def reference_arm(geo, args, log):
@@ -473,6 +475,12 @@ def main():
             run_kmeans(geo, args, log)
         return
     run_decode(geo, args, rank, world, local_rank, log)
+    if world > 1:
+        # leave without tearing the NCCL communicator down (its teardown after graph-captured
+        # collectives did not return on this pool); everything has been printed and flushed
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
