@@ -1,0 +1,397 @@
+// attend: split-K weighted flash decoding over (a) the estimation set — every estimated cluster is
+// one row: score from the scan, value = the cluster's value sum, weight = cluster size in the
+// softmax denominator — and (b) the exact set — steady zone followed by the retrieved clusters, read
+// in place from the cluster-contiguous KV store through the row list.  All partial results of a
+// group are merged by log-sum-exp in the last chunk of the group to finish.
+// (reference: the two weighted_flash_decoding calls, cache_hub/retroinfer_cache.py:611-617 and
+// :666-674, with gather_copy_vectors :601-605 and gather_copy_and_concat :642-648 in between).
+//
+// One CTA = 4 independent warps x 4 steps of 16 rows = 256 rows.  Each lane fetches the ids of all
+// rows it will touch up front, then streams its 16-byte pieces of K and V through a lane-private
+// two-stage cp.async ring in shared memory (256 bytes per lane and step), so two steps of loads
+// are always in flight per warp while the tensor cores work on the current one.
+//
+// Tensor-core use: m16n8k16 MMA.  QK^T has the GQA group in M and 8 rows in N, with the same
+// channel permutation on both operands as in the scan.  PV is computed transposed (16 channels in
+// M, the 8 heads in N, 16 rows in K): lane (r, t) owns rows tt = {2t, 2t+1, 8+2t, 9+2t} of the step
+// and, of each, the 16-byte pieces r and r+8 (channels 8r..8r+7 and 64+8r..64+8r+7).  O^T tile x
+// takes channel word x of those pieces: low halves are MMA rows r, high halves rows r+8, so tile x,
+// row r is channel ch(x) = (x<4 ? 8r+2x : 64+8r+2(x-4)) and row r+8 is ch(x)+1.  The probabilities
+// come straight from the QK^T accumulators as the B fragment.
+#include "ri_wave_internal.cuh"
+
+namespace ri_wave {
+namespace {
+
+constexpr int kSteps = kAttendChunk / 4 / 16;   // steps per warp
+constexpr int kStages = 2;
+constexpr int kStageBytes = 16 * 32 * 16;       // 16 pieces x 32 lanes x 16 bytes = 8 KB per warp and stage
+constexpr int kAttendSmem = 4 * kStages * kStageBytes;
+
+struct AttendArgs {
+  const uint4* q;
+  const uint4* keys;
+  const uint4* values;
+  const uint4* steady_k;
+  const uint4* steady_v;
+  const uint4* value_sum;
+  const int32_t* static_len;
+  const int32_t* rows;
+  const int32_t* n_exact;
+  const int32_t* est_ids;
+  const float* est_w;
+  const float* est_s2;
+  float* part_o;
+  float* part_m;
+  float* part_l;
+  uint32_t* counters;
+  void* out;
+  int64_t N;
+  int C, gs, E, e_pad, est_chunks, n_chunks, steady_stride, max_rows;
+  float scale2;   // log2(e) / sqrt(d)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int DT>
+__device__ __forceinline__ void pv_step(float (&acc)[8][4], const uint4 (&v)[4][2], uint32_t b0, uint32_t b1) {
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const int piece = x >> 2, w = x & 3;
+    const uint32_t t0 = (&v[0][piece].x)[w], t1 = (&v[1][piece].x)[w];
+    const uint32_t t2 = (&v[2][piece].x)[w], t3 = (&v[3][piece].x)[w];
+    const uint32_t a0 = __byte_perm(t0, t1, 0x5410), a1 = __byte_perm(t0, t1, 0x7632);
+    const uint32_t a2 = __byte_perm(t2, t3, 0x5410), a3 = __byte_perm(t2, t3, 0x7632);
+    Elem<DT>::mma16816(acc[x], a0, a1, a2, a3, b0, b1);
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(128, 3) wave_attend_kernel(AttendArgs a) {
+  const int g = blockIdx.y, chunk = blockIdx.x;
+  const int static_len = *a.static_len;
+  const int n_ret = a.n_exact[g];
+  const int total_exact = static_len + n_ret;
+  const int n_active = a.est_chunks + (total_exact + kAttendChunk - 1) / kAttendChunk;
+  if (chunk >= n_active) return;
+
+  extern __shared__ __align__(16) uint8_t ring[];
+  __shared__ float sm_m[4][kMaxHeads], sm_l[4][kMaxHeads];
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, t = lane & 3;
+  const int gs = a.gs;
+  const bool is_est = chunk < a.est_chunks;
+  const int rows_end = is_est ? a.E : total_exact;
+  const int warp_base = (is_est ? chunk : chunk - a.est_chunks) * kAttendChunk + warp * (kAttendChunk / 4);
+  const int last = rows_end - 1;
+  const int n_steps = warp_base >= rows_end ? 0 : min(kSteps, (rows_end - warp_base + 15) / 16);
+  // this lane's slots: ring + ((warp*kStages + stage)*16 + piece)*512 + lane*16
+  const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStages * kStageBytes + lane * 16;
+
+  // ---- ids of every row this lane touches (>= 0: row of the KV store / cluster id; < 0: steady row) ----
+  int kid[kSteps][2], vid[kSteps][4];
+  {
+    const int tt[4] = {2 * t, 2 * t + 1, 8 + 2 * t, 9 + 2 * t};
+#pragma unroll
+    for (int s = 0; s < kSteps; ++s) {
+      const int base = warp_base + s * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = min(base + tt[i], last);
+        int id = 0;
+        if (s < n_steps) {
+          if (is_est) id = a.est_ids[(int64_t)g * a.e_pad + row];
+          else id = row < static_len ? -1 - row : a.rows[(int64_t)g * a.max_rows + row - static_len];
+        }
+        vid[s][i] = id;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int row = min(base + j * 8 + r, last);
+        int id = 0;
+        if (s < n_steps && !is_est)
+          id = row < static_len ? -1 - row : a.rows[(int64_t)g * a.max_rows + row - static_len];
+        kid[s][j] = id;
+      }
+    }
+  }
+
+  auto issue = [&](int s) {
+    const uint32_t dst = my_ring + (s % kStages) * kStageBytes;
+    if (is_est) {
+      // pieces 0/1: this lane's scores and weights of the step; pieces 8..15: value-sum rows
+      const int i0 = warp_base + s * 16 + 2 * t;
+      if (r < gs) {
+        const float* sp = a.est_s2 + ((int64_t)g * kMaxHeads + r) * a.e_pad + i0;
+        cp_async8(dst, sp);
+        cp_async8(dst + 8, sp + 8);
+      }
+      const float* wp = a.est_w + (int64_t)g * a.e_pad + i0;
+      cp_async8(dst + 512, wp);
+      cp_async8(dst + 512 + 8, wp + 8);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4* p = a.value_sum + ((int64_t)g * a.C + vid[s][i]) * 16;
+        cp_async16(dst + (8 + 2 * i) * 512, p + r);
+        cp_async16(dst + (9 + 2 * i) * 512, p + r + 8);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int id = kid[s][j];
+        const uint4* p = id < 0 ? a.steady_k + ((int64_t)g * a.steady_stride + (-1 - id)) * 16
+                                : a.keys + ((int64_t)g * a.N + id) * 16;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) cp_async16(dst + (4 * j + kk) * 512, p + t + kk * 4);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int id = vid[s][i];
+        const uint4* p = id < 0 ? a.steady_v + ((int64_t)g * a.steady_stride + (-1 - id)) * 16
+                                : a.values + ((int64_t)g * a.N + id) * 16;
+        cp_async16(dst + (8 + 2 * i) * 512, p + r);
+        cp_async16(dst + (9 + 2 * i) * 512, p + r + 8);
+      }
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) {
+    if (s < n_steps) issue(s);
+    cp_async_commit();
+  }
+
+  uint4 qa[4];
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk)
+    qa[kk] = (!is_est && r < gs) ? ri_ldg16(a.q + ((int64_t)g * gs + r) * 16 + t + kk * 4) : make_uint4(0, 0, 0, 0);
+
+  float acc[8][4];
+#pragma unroll
+  for (int x = 0; x < 8; ++x)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[x][i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;   // head r (l: this lane's share, reduced over the quad at the end)
+
+#pragma unroll
+  for (int s = 0; s < kSteps; ++s) {
+    if (s < n_steps) {
+      cp_async_wait<kStages - 1>();       // the group of step s has landed (lane-private slots: no barrier)
+      const uint8_t* src = ring + warp * kStages * kStageBytes + (s % kStages) * kStageBytes + lane * 16;
+      const int base = warp_base + s * 16;
+
+      float s2[2][2];
+      float w[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+      if (is_est) {
+        const float4 sv = *reinterpret_cast<const float4*>(src);
+        const float4 wv = *reinterpret_cast<const float4*>(src + 512);
+        const bool head = r < gs;
+        s2[0][0] = head ? sv.x : -INFINITY; s2[0][1] = head ? sv.y : -INFINITY;
+        s2[1][0] = head ? sv.z : -INFINITY; s2[1][1] = head ? sv.w : -INFINITY;
+        w[0][0] = wv.x; w[0][1] = wv.y; w[1][0] = wv.z; w[1][1] = wv.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint4 kb = *reinterpret_cast<const uint4*>(src + (4 * j + kk) * 512);
+            Elem<DT>::mma16816(c, qa[kk].x, 0u, qa[kk].y, 0u, kb.x, kb.y);
+            Elem<DT>::mma16816(c, qa[kk].z, 0u, qa[kk].w, 0u, kb.z, kb.w);
+          }
+          s2[j][0] = c[0] * a.scale2;
+          s2[j][1] = c[1] * a.scale2;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (base + j * 8 + 2 * t + e >= rows_end) { s2[j][e] = -INFINITY; w[j][e] = 0.f; }
+
+      // online softmax for head r
+      float mx = fmaxf(fmaxf(s2[0][0], s2[0][1]), fmaxf(s2[1][0], s2[1][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_safe);   // m_run = -inf -> 0
+      float p[2][2];
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[j][e] = exp2f(s2[j][e] - m_safe);
+          psum += p[j][e] * w[j][e];
+        }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+      // the accumulators hold heads 2t and 2t+1: fetch their rescale factors from the quads that own them
+      const float f0 = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4);
+      const float f1 = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) { acc[x][0] *= f0; acc[x][1] *= f1; acc[x][2] *= f0; acc[x][3] *= f1; }
+      uint4 v[4][2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i][0] = *reinterpret_cast<const uint4*>(src + (8 + 2 * i) * 512);
+        v[i][1] = *reinterpret_cast<const uint4*>(src + (9 + 2 * i) * 512);
+      }
+      pv_step<DT>(acc, v, Elem<DT>::pack2(p[0][0], p[0][1]), Elem<DT>::pack2(p[1][0], p[1][1]));
+      if (s + kStages < n_steps) issue(s + kStages);   // refill the slot just consumed (same lane wrote and read it)
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+  // ---- merge the four warps of this chunk ----
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (t == 0) { sm_m[warp][r] = m_run; sm_l[warp][r] = l_run; }
+  // each warp parks its 8 x 128 accumulator in its own (now idle) ring region
+  auto warp_o = [&](int w) { return reinterpret_cast<float*>(ring + w * kStages * kStageBytes); };
+  {
+    float* my_o = warp_o(warp);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const int ch = (x < 4) ? 8 * r + 2 * x : 64 + 8 * r + 2 * (x - 4);
+      my_o[(2 * t) * RI_HEAD_DIM + ch] = acc[x][0];
+      my_o[(2 * t + 1) * RI_HEAD_DIM + ch] = acc[x][1];
+      my_o[(2 * t) * RI_HEAD_DIM + ch + 1] = acc[x][2];
+      my_o[(2 * t + 1) * RI_HEAD_DIM + ch + 1] = acc[x][3];
+    }
+  }
+  __syncthreads();
+  const int64_t pbase = (int64_t)g * a.n_chunks + chunk;
+  for (int h = 0; h < gs; ++h) {
+    const float M = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+      const float f = exp2f(sm_m[wi][h] - Ms);
+      L += sm_l[wi][h] * f;
+      O += warp_o(wi)[h * RI_HEAD_DIM + tid] * f;
+    }
+    a.part_o[(pbase * gs + h) * RI_HEAD_DIM + tid] = O;
+    if (tid == 0) { a.part_m[pbase * kMaxHeads + h] = M; a.part_l[pbase * kMaxHeads + h] = L; }
+  }
+
+  // ---- the last chunk of the group to arrive combines all partial results ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t ticket = atomicAdd(&a.counters[g], 1u);
+    s_last = ticket == (uint32_t)(n_active - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int64_t gbase = (int64_t)g * a.n_chunks;
+  // All loads below are independent of one another, so the whole merge costs a few L2 round trips.
+  // Tables (n_active <= kMaxChunks rows of 8 heads, 16 KB) reuse the ring.
+  float* tf = reinterpret_cast<float*>(ring);    // running max, then the rescale factor 2^(m - M)
+  float* tl = tf + kMaxChunks * kMaxHeads;       // denominators
+  for (int i = tid; i < n_active * kMaxHeads; i += 128) {
+    tf[i] = __ldcg(a.part_m + gbase * kMaxHeads + i);
+    tl[i] = __ldcg(a.part_l + gbase * kMaxHeads + i);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {               // warp w reduces heads 2w and 2w+1
+    const int h = warp * 2 + hh;
+    float M = -INFINITY;
+    for (int c = lane; c < n_active; c += 32) M = fmaxf(M, tf[c * kMaxHeads + h]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+    for (int c = lane; c < n_active; c += 32) {
+      const float f = exp2f(tf[c * kMaxHeads + h] - Ms);
+      tf[c * kMaxHeads + h] = f;
+      L += tl[c * kMaxHeads + h] * f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) sm_l[0][h] = L;
+  }
+  __syncthreads();
+  const int dq = tid >> 2, cl = tid & 3;         // 4 channels per thread, chunks split 4 ways
+  for (int h = 0; h < gs; ++h) {
+    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int c = cl; c < n_active; c += 4) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_o + ((gbase + c) * gs + h) * RI_HEAD_DIM) + dq);
+      const float f = tf[c * kMaxHeads + h];
+      o4.x += v.x * f; o4.y += v.y * f; o4.z += v.z * f; o4.w += v.w * f;
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      o4.x += __shfl_xor_sync(0xffffffffu, o4.x, o);
+      o4.y += __shfl_xor_sync(0xffffffffu, o4.y, o);
+      o4.z += __shfl_xor_sync(0xffffffffu, o4.z, o);
+      o4.w += __shfl_xor_sync(0xffffffffu, o4.w, o);
+    }
+    if (cl == 0) {
+      const float L = sm_l[0][h];
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+      uint2 o2;
+      o2.x = Elem<DT>::pack2(o4.x * inv, o4.y * inv);
+      o2.y = Elem<DT>::pack2(o4.z * inv, o4.w * inv);
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + ((int64_t)g * gs + h) * RI_HEAD_DIM + 4 * dq) = o2;
+    }
+  }
+  if (tid == 0) a.counters[g] = 0u;   // leave the scratch reusable
+}
+
+template <int DT>
+int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
+  uint8_t* sc = static_cast<uint8_t*>(p.d_scratch);
+  AttendArgs a;
+  a.q = static_cast<const uint4*>(p.d_q);
+  a.keys = static_cast<const uint4*>(p.d_keys);
+  a.values = static_cast<const uint4*>(p.d_values);
+  a.steady_k = static_cast<const uint4*>(p.d_steady_keys);
+  a.steady_v = static_cast<const uint4*>(p.d_steady_values);
+  a.value_sum = static_cast<const uint4*>(p.d_value_sum);
+  a.static_len = p.d_static_len;
+  a.rows = reinterpret_cast<const int32_t*>(sc + L.rows);
+  a.n_exact = reinterpret_cast<const int32_t*>(sc + L.n_exact);
+  a.est_ids = reinterpret_cast<const int32_t*>(sc + L.est_ids);
+  a.est_w = reinterpret_cast<const float*>(sc + L.est_w);
+  a.est_s2 = reinterpret_cast<const float*>(sc + L.est_s2);
+  a.part_o = reinterpret_cast<float*>(sc + L.part_o);
+  a.part_m = reinterpret_cast<float*>(sc + L.part_m);
+  a.part_l = reinterpret_cast<float*>(sc + L.part_l);
+  a.counters = reinterpret_cast<uint32_t*>(sc + L.counters);
+  a.out = p.d_out;
+  a.N = p.tokens_per_group;
+  a.C = p.n_centroids; a.gs = p.group_size; a.E = p.n_estimate; a.e_pad = L.e_pad;
+  a.est_chunks = L.est_chunks; a.n_chunks = L.n_chunks; a.steady_stride = p.steady_stride;
+  a.max_rows = p.max_exact_rows;
+  a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  RI_REQUIRE(L.n_chunks <= kMaxChunks, "geometry needs %d attention chunks per group, the merge handles %d",
+             L.n_chunks, kMaxChunks);
+  RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttendSmem));
+  wave_attend_kernel<DT><<<dim3(L.n_chunks, p.groups), 128, kAttendSmem, s>>>(a);
+  RI_LAUNCH_OK("wave_attend_kernel");
+  return RI_OK;
+}
+
+}  // namespace
+
+int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
+  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s) : launch<RI_F16>(p, L, s);
+}
+
+}  // namespace ri_wave
