@@ -199,28 +199,45 @@ def algorithmic_bytes(wl, n_ret_rows, static_len):
 
 
 def time_stages(wl, first_step, steps):
-    """Average device time of each kernel: CUDA events around every launch in an eager pass."""
+    """Device time of each stage, averaged over layers and steps.  Three CUDA graphs replay the
+    stage prefixes scan / scan+select / scan+select+attend over ALL layers (so every launch works
+    on cold data, as in the real step, and no host launch gap is timed); a stage's time is the
+    difference between consecutive prefixes, so the three numbers add up to the attention part of
+    the step."""
     names = ("scan", "select", "attend")
-    ev = {n: [] for n in names}
-    n_ret = 0
-    for st in range(first_step, first_step + steps):
-        wl.q_in.copy_(wl.q_all[st]); wl.k_in.copy_(wl.k_all[st]); wl.v_in.copy_(wl.v_all[st])
-        for l in range(wl.geo.layers):
-            wl.cache.decode_update_kv_cache(wl.k_in[l], wl.v_in[l], l)
-            layer = wl.cache._layers[l]
-            for n in names:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
+    layers = wl.cache._layers
+    graphs = []
+    wl.q_in.copy_(wl.q_all[first_step]); wl.k_in.copy_(wl.k_all[first_step]); wl.v_in.copy_(wl.v_all[first_step])
+    for upto in range(1, 4):
+        for l, layer in enumerate(layers):           # warm (and validate) outside capture
+            for n in names[:upto]:
                 layer.stage(n, wl.q_in[l], wl.out[l])
-                b.record()
-                ev[n].append((a, b))
-            if st == first_step + steps - 1:
-                n_ret += int(layer.views()["n_exact"].sum().item())
-        static_len = wl.static_len()
-        wl.cache._per_device[str(wl.device)]["static_len"].add_(1)
-    torch.cuda.synchronize()
-    ms = {n: sum(a.elapsed_time(b) for a, b in ev[n]) / len(ev[n]) for n in names}
-    return ms, n_ret / wl.geo.layers, static_len
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for l, layer in enumerate(layers):
+                for n in names[:upto]:
+                    layer.stage(n, wl.q_in[l], wl.out[l])
+        graphs.append(g)
+    prefix_ms = []
+    for g in graphs:
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for st in range(steps):
+            wl.q_in.copy_(wl.q_all[first_step + st])
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        prefix_ms.append(a.elapsed_time(b) / (steps * len(layers)))
+    ms = {"scan": prefix_ms[0], "select": prefix_ms[1] - prefix_ms[0], "attend": prefix_ms[2] - prefix_ms[1]}
+    n_ret = 0
+    for l, layer in enumerate(layers):
+        for n in names[:2]:
+            layer.stage(n, wl.q_in[l], wl.out[l])
+        n_ret += int(layer.views()["n_exact"].sum().item())
+    return ms, n_ret / len(layers), wl.static_len()
 
 
 def cpu_layer_seconds(wl, layer_idx, step, repeats):

@@ -65,19 +65,46 @@ __device__ __forceinline__ uint32_t block_scan(uint32_t v, uint32_t* warp_sums, 
   return base + inc - v;
 }
 
-// hist: 256 bins summed over the cluster (bin 255 = largest keys); local: this CTA's own bins.
-// Finds the bin where the count from the top first reaches `k` (k >= 1 or the call is skipped by
-// passing k <= 0).  out[0] = bin, out[1] = cluster-wide count above it, out[2] = this CTA's count
-// above it.  All 256 threads call.
-__device__ __forceinline__ void find_bin(const int* hist, const int* local, int k, int* out, uint32_t* warp_sums) {
-  const int bin = 255 - threadIdx.x;
-  const uint32_t cnt = (uint32_t)hist[bin];
-  uint32_t total;
-  const uint32_t above = block_scan(cnt, warp_sums, total);
-  const uint32_t above_local = block_scan((uint32_t)local[bin], warp_sums, total);
-  if (k > 0 && (int)above < k && (int)(above + cnt) >= k) out[0] = bin;
+__device__ __forceinline__ uint64_t block_scan64(uint64_t v, uint64_t* warp_sums, uint64_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint64_t n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
   __syncthreads();
-  if (bin == out[0]) { out[1] = (int)above; out[2] = (int)above_local; }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  uint64_t base = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kSelectThreads / 32; ++w) {
+    const uint64_t x = warp_sums[w];
+    if (w < warp) base += x;
+    tot += x;
+  }
+  total = tot;
+  return base + inc - v;
+}
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// Two histograms of 256 bins (bin 255 = largest keys), each given as the cluster-wide sum (ga, gb)
+// and this CTA's own counts (la, lb); counts fit 16 bits.  For histogram a find the bin where the
+// count from the top first reaches ka (>= 1), likewise b/kb, with ONE packed scan.
+// out?[0] = bin, out?[1] = cluster-wide count above it, out?[2] = this CTA's count above it.
+__device__ __forceinline__ void find_bins(const int* ga, const int* la, int ka, int* outa, const int* gb,
+                                          const int* lb, int kb, int* outb, uint64_t* warp_sums) {
+  const int bin = 255 - threadIdx.x;
+  const uint64_t ca = (uint64_t)ga[bin], cb = (uint64_t)gb[bin];
+  const uint64_t v = ca | ((uint64_t)la[bin] << 16) | (cb << 32) | ((uint64_t)lb[bin] << 48);
+  uint64_t total;
+  const uint64_t pre = block_scan64(v, warp_sums, total);
+  const int above_a = (int)(pre & 0xffffu), above_la = (int)((pre >> 16) & 0xffffu);
+  const int above_b = (int)((pre >> 32) & 0xffffu), above_lb = (int)(pre >> 48);
+  if (above_a < ka && above_a + (int)ca >= ka) { outa[0] = bin; outa[1] = above_a; outa[2] = above_la; }
+  if (above_b < kb && above_b + (int)cb >= kb) { outb[0] = bin; outb[1] = above_b; outb[2] = above_lb; }
   __syncthreads();
 }
 
@@ -91,11 +118,12 @@ wave_select_kernel(SelectArgs a) {
   uint32_t* ranked = cand + a.p_pad;                                                   // [p_pad]
   uint32_t* rstart = ranked + a.p_pad;                                                 // [p_pad]
 
-  __shared__ int hist1[256], hist2a[256], hist2b[256], hsum[256];
+  __shared__ int hist1[256], hist2a[256], hist2b[256], hsum[256], hsum2[256];
   __shared__ float s_max[kMaxHeads], s_inv[kMaxHeads];
   __shared__ int s_pub[2];          // this CTA's (clusters in top P+E, clusters in top P)
   __shared__ int fk[3], fp[3], lk[3], lp[3];
   __shared__ uint32_t warp_sums[kSelectThreads / 32];
+  __shared__ uint64_t warp_sums64[kSelectThreads / 32];
   __shared__ int s_keep, s_rows;
 
   const int rank = (int)cluster.block_rank();
@@ -149,10 +177,6 @@ wave_select_kernel(SelectArgs a) {
       keys[e + i] = k4[i];
       atomicAdd(&hist1[k4[i] >> 8], 1);
     }
-    uint2 kw;
-    kw.x = (uint32_t)k4[0] | ((uint32_t)k4[1] << 16);
-    kw.y = (uint32_t)k4[2] | ((uint32_t)k4[3] << 16);
-    *reinterpret_cast<uint2*>(a.dist_keys + (int64_t)g * C + c) = kw;
   }
   __syncthreads();
   cluster.sync();
@@ -166,8 +190,7 @@ wave_select_kernel(SelectArgs a) {
     hsum[tid] = s;
   }
   __syncthreads();
-  find_bin(hsum, hist1, K, fk, warp_sums);
-  find_bin(hsum, hist1, a.P, fp, warp_sums);
+  find_bins(hsum, hist1, K, fk, hsum, hist1, a.P, fp, warp_sums64);
   const int binK = fk[0], binP = fp[0];
 
   // ---- 3b. low byte ----
@@ -179,22 +202,17 @@ wave_select_kernel(SelectArgs a) {
   __syncthreads();
   cluster.sync();
   {
-    int s = 0;
+    int sa = 0, sb = 0;
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) s += cluster.map_shared_rank(hist2a, rr)[tid];
-    hsum[tid] = s;
+    for (int rr = 0; rr < kSelectCluster; ++rr) {
+      sa += cluster.map_shared_rank(hist2a, rr)[tid];
+      sb += cluster.map_shared_rank(hist2b, rr)[tid];
+    }
+    hsum[tid] = sa;
+    hsum2[tid] = sb;
   }
   __syncthreads();
-  find_bin(hsum, hist2a, K - fk[1], lk, warp_sums);
-  {
-    int s = 0;
-#pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) s += cluster.map_shared_rank(hist2b, rr)[tid];
-    __syncthreads();
-    hsum[tid] = s;
-  }
-  __syncthreads();
-  find_bin(hsum, hist2b, a.P - fp[1], lp, warp_sums);
+  find_bins(hsum, hist2a, K - fk[1], lk, hsum2, hist2b, a.P - fp[1], lp, warp_sums64);
   const uint16_t TK = (uint16_t)((binK << 8) | lk[0]), TP = (uint16_t)((binP << 8) | lp[0]);
   const int needK = K - fk[1] - lk[1];      // how many keys equal to TK are taken (cluster-wide)
   const int needP = a.P - fp[1] - lp[1];
@@ -251,6 +269,17 @@ wave_select_kernel(SelectArgs a) {
     uint32_t sel_total;
     const uint32_t sel_pre = block_scan(sel, warp_sums, sel_total);
     int pe = est_base + (int)(sel_pre & 0xffffu), pr = ret_base + (int)(sel_pre >> 16);
+    // retrieval candidates first (shared memory of CTA 0) ...
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (isRet[i]) {
+        if (pr < a.P) cand0[pr] = ((uint32_t)k4[i] << 16) | (uint32_t)(0xffff - (lo + e + i));
+        ++pr;
+      }
+    est_base += (int)(sel_total & 0xffffu);
+    ret_base += (int)(sel_total >> 16);
+    const bool last_round = e0 + kSelectThreads * 4 >= n_loc;
+    if (last_round) cluster_arrive();   // ... so the barrier's release does not wait for the global stores below
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int c = lo + e + i;
@@ -265,15 +294,10 @@ wave_select_kernel(SelectArgs a) {
         }
         ++pe;
       }
-      if (isRet[i]) {
-        if (pr < a.P) cand0[pr] = ((uint32_t)k4[i] << 16) | (uint32_t)(0xffff - c);
-        ++pr;
-      }
     }
-    est_base += (int)(sel_total & 0xffffu);
-    ret_base += (int)(sel_total >> 16);
   }
-  cluster.sync();
+  if (n_loc <= 0) cluster_arrive();     // a CTA with an empty slice never entered the loop
+  cluster_wait();
 
   // ---- 5. CTA 0: rank the candidates, page budget, place of each kept cluster in the row list ----
   if (rank == 0) {
@@ -294,7 +318,6 @@ wave_select_kernel(SelectArgs a) {
       cnt[u] = in ? a.count[(int64_t)g * C + cid] : 0;
       pages[u] = (cnt[u] + a.page - 1) / a.page;
       psum += (uint32_t)pages[u];
-      if (in && a.retrieved_ids) a.retrieved_ids[(int64_t)g * a.P + i] = cid;
     }
     uint32_t total;
     uint32_t before = block_scan(psum, warp_sums, total);
@@ -308,26 +331,36 @@ wave_select_kernel(SelectArgs a) {
       nfit += fits[u] ? 1u : 0u;
       rsum += fits[u] ? (uint32_t)cnt[u] : 0u;
     }
-    uint32_t kept_total, rows_total;
-    block_scan(nfit, warp_sums, kept_total);
-    uint32_t row_start = block_scan(rsum, warp_sums, rows_total);
+    // kept count (<= 1024) in the high 12 bits, kept rows (< 2^20) in the low 20
+    uint32_t both_total;
+    const uint32_t both_pre = block_scan((nfit << 20) | rsum, warp_sums, both_total);
+    uint32_t row_start = both_pre & 0xfffffu;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = tid * 4 + u;
       if (i < a.P) rstart[i] = row_start;
       row_start += fits[u] ? (uint32_t)cnt[u] : 0u;
     }
-    if (tid == 0) {
-      s_keep = (int)kept_total;
-      s_rows = (int)rows_total;
-      a.n_exact[g] = (int)rows_total;
-      if (a.retrieved_kept) a.retrieved_kept[g] = (int)kept_total;
-    }
+    if (tid == 0) { s_keep = (int)(both_total >> 20); s_rows = (int)(both_total & 0xfffffu); }
     __syncthreads();
   }
   cluster.sync();
 
   // ---- 6. all CTAs expand the kept clusters into row indices ----
+  for (int e = tid * 4; e < n_loc; e += kSelectThreads * 4) {   // the 16-bit distance keys (a view for tests)
+    uint2 kw;
+    kw.x = (uint32_t)keys[e] | ((uint32_t)keys[e + 1] << 16);
+    kw.y = (uint32_t)keys[e + 2] | ((uint32_t)keys[e + 3] << 16);
+    *reinterpret_cast<uint2*>(a.dist_keys + (int64_t)g * C + lo + e) = kw;
+  }
+  if (rank == 0) {
+    if (tid == 0) {
+      a.n_exact[g] = s_rows;
+      if (a.retrieved_kept) a.retrieved_kept[g] = s_keep;
+    }
+    if (a.retrieved_ids)
+      for (int i = tid; i < a.P; i += kSelectThreads) a.retrieved_ids[(int64_t)g * a.P + i] = 0xffff - (int)(ranked[i] & 0xffffu);
+  }
   {
     const int keep = *cluster.map_shared_rank(&s_keep, 0);
     const uint32_t* ranked0 = cluster.map_shared_rank(ranked, 0);
@@ -367,6 +400,7 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   a.page = p.page_size; a.buffer_pages = p.buffer_pages; a.max_rows = p.max_exact_rows; a.n_tiles = L.n_tiles;
   a.slice = ((p.n_centroids / 8 + kSelectCluster - 1) / kSelectCluster) * 8;
   a.p_pad = (int)ri_align_up(p.nprobe, 4);
+  RI_REQUIRE(p.max_exact_rows < (1 << 20), "max_exact_rows=%d too large (limit 2^20 - 1)", p.max_exact_rows);
   const size_t smem = ri_align16((size_t)a.slice * 2) + (size_t)a.p_pad * 12;
   if (smem > 48 * 1024)
     RI_CUDA_OK(cudaFuncSetAttribute(wave_select_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
