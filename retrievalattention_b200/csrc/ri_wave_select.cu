@@ -87,8 +87,14 @@ __device__ __forceinline__ uint64_t block_scan64(uint64_t v, uint64_t* warp_sums
   return base + inc - v;
 }
 
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive() {
+  __syncwarp();   // .aligned: the whole warp must execute the instruction together
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  __syncwarp();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 // Two histograms of 256 bins (bin 255 = largest keys), each given as the cluster-wide sum (ga, gb)
 // and this CTA's own counts (la, lb); counts fit 16 bits.  For histogram a find the bin where the
@@ -115,8 +121,12 @@ wave_select_kernel(SelectArgs a) {
   extern __shared__ __align__(16) uint8_t dyn[];
   uint16_t* keys = reinterpret_cast<uint16_t*>(dyn);                                   // [slice]
   uint32_t* cand = reinterpret_cast<uint32_t*>(dyn + ri_align16((size_t)a.slice * 2)); // [p_pad] (used in CTA 0)
-  uint32_t* ranked = cand + a.p_pad;                                                   // [p_pad]
-  uint32_t* rstart = ranked + a.p_pad;                                                 // [p_pad]
+  uint32_t* cand_cnt = cand + a.p_pad;      // size and first row of each candidate, written by its owner
+  uint32_t* cand_off = cand_cnt + a.p_pad;
+  uint32_t* ranked = cand_off + a.p_pad;    // the same three, in rank order, plus the place in the row list
+  uint32_t* rcnt = ranked + a.p_pad;
+  uint32_t* roff = rcnt + a.p_pad;
+  uint32_t* rstart = roff + a.p_pad;
 
   __shared__ int hist1[256], hist2a[256], hist2b[256], hsum[256], hsum2[256];
   __shared__ float s_max[kMaxHeads], s_inv[kMaxHeads];
@@ -138,17 +148,20 @@ wave_select_kernel(SelectArgs a) {
   if (warp < gs) {
     const float* tm = a.tile_max + ((int64_t)g * kMaxHeads + warp) * a.n_tiles;
     const float* ts = a.tile_sum + ((int64_t)g * kMaxHeads + warp) * a.n_tiles;
-    float M = -INFINITY;
-    for (int i = lane; i < a.n_tiles; i += 32) M = fmaxf(M, tm[i]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float S = 0.f;
+    float M = -INFINITY, S = 0.f;           // running (max, sum) pair, merged pairwise
     for (int i = lane; i < a.n_tiles; i += 32) {
-      const float m = tm[i];
-      if (m > -INFINITY) S += ts[i] * exp2f((m - M) * RI_LOG2E);
+      const float m = tm[i], sv = ts[i];
+      const float Mn = fmaxf(M, m);
+      if (Mn > -INFINITY) S = S * exp2f((M - Mn) * RI_LOG2E) + sv * exp2f((m - Mn) * RI_LOG2E);
+      M = Mn;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) S += __shfl_xor_sync(0xffffffffu, S, o);
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, M, o), s2 = __shfl_xor_sync(0xffffffffu, S, o);
+      const float Mn = fmaxf(M, m2);
+      if (Mn > -INFINITY) S = S * exp2f((M - Mn) * RI_LOG2E) + s2 * exp2f((m2 - Mn) * RI_LOG2E);
+      M = Mn;
+    }
     if (lane == 0) { s_max[warp] = M; s_inv[warp] = 1.0f / S; }
   }
   __syncthreads();
@@ -239,30 +252,46 @@ wave_select_kernel(SelectArgs a) {
 
   // ---- 4. ordered compaction ----
   uint32_t* cand0 = cluster.map_shared_rank(cand, 0);
+  uint32_t* cand_cnt0 = cluster.map_shared_rank(cand_cnt, 0);
+  uint32_t* cand_off0 = cluster.map_shared_rank(cand_off, 0);
   for (int e0 = 0; e0 < n_loc; e0 += kSelectThreads * 4) {
     const int e = e0 + tid * 4;
+    const bool quad = e < n_loc;            // slices are multiples of 4: a quad is entirely in or out
+    // what an estimation entry needs, fetched coalesced up front (the scans below hide the latency)
+    float4 s4[kMaxHeads];
+    uint2 sz = make_uint2(0u, 0u);
+    if (quad) {
+#pragma unroll
+      for (int h = 0; h < kMaxHeads; ++h)
+        if (h < gs) s4[h] = *reinterpret_cast<const float4*>(sc + (int64_t)h * C + lo + e);
+      sz = *reinterpret_cast<const uint2*>(a.size_dt + (int64_t)g * C + lo + e);
+    }
     uint16_t k4[4];
     uint32_t eq = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      k4[i] = e + i < n_loc ? keys[e + i] : (uint16_t)0;
-      if (e + i < n_loc) eq += (k4[i] == TK ? 1u : 0u) | (k4[i] == TP ? 0x10000u : 0u);
+      k4[i] = quad ? keys[e + i] : (uint16_t)0;
+      if (quad) eq += (k4[i] == TK ? 1u : 0u) | (k4[i] == TP ? 0x10000u : 0u);
     }
     uint32_t eq_total;
     const uint32_t eq_pre = block_scan(eq, warp_sums, eq_total);
     int rkK = tieK_base + (int)(eq_pre & 0xffffu), rkP = tieP_base + (int)(eq_pre >> 16);
     bool isEst[4], isRet[4];
+    int rcount[4] = {0, 0, 0, 0}, roffset[4] = {0, 0, 0, 0};
     uint32_t sel = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const bool in = e + i < n_loc;
-      const bool inK = in && (k4[i] > TK || (k4[i] == TK && rkK < needK));
-      const bool inP = in && (k4[i] > TP || (k4[i] == TP && rkP < needP));
-      if (in && k4[i] == TK) ++rkK;
-      if (in && k4[i] == TP) ++rkP;
+      const bool inK = quad && (k4[i] > TK || (k4[i] == TK && rkK < needK));
+      const bool inP = quad && (k4[i] > TP || (k4[i] == TP && rkP < needP));
+      if (quad && k4[i] == TK) ++rkK;
+      if (quad && k4[i] == TP) ++rkP;
       isRet[i] = inP;
       isEst[i] = inK && !inP;
       sel += (isEst[i] ? 1u : 0u) | (isRet[i] ? 0x10000u : 0u);
+      if (inP) {                            // travels with the candidate: no gather later
+        rcount[i] = a.count[(int64_t)g * C + lo + e + i];
+        roffset[i] = a.offset[(int64_t)g * (C + 1) + lo + e + i];
+      }
     }
     tieK_base += (int)(eq_total & 0xffffu);
     tieP_base += (int)(eq_total >> 16);
@@ -273,24 +302,28 @@ wave_select_kernel(SelectArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       if (isRet[i]) {
-        if (pr < a.P) cand0[pr] = ((uint32_t)k4[i] << 16) | (uint32_t)(0xffff - (lo + e + i));
+        if (pr < a.P) {
+          cand0[pr] = ((uint32_t)k4[i] << 16) | (uint32_t)(0xffff - (lo + e + i));
+          cand_cnt0[pr] = (uint32_t)rcount[i];
+          cand_off0[pr] = (uint32_t)roffset[i];
+        }
         ++pr;
       }
     est_base += (int)(sel_total & 0xffffu);
     ret_base += (int)(sel_total >> 16);
     const bool last_round = e0 + kSelectThreads * 4 >= n_loc;
     if (last_round) cluster_arrive();   // ... so the barrier's release does not wait for the global stores below
+    const uint32_t szw[2] = {sz.x, sz.y};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int c = lo + e + i;
       if (isEst[i]) {
         if (pe < a.E) {
-          a.est_ids[(int64_t)g * a.e_pad + pe] = c;
-          a.est_w[(int64_t)g * a.e_pad + pe] = Elem<DT>::from_bits(a.size_dt[(int64_t)g * C + c]);
+          a.est_ids[(int64_t)g * a.e_pad + pe] = lo + e + i;
+          a.est_w[(int64_t)g * a.e_pad + pe] = Elem<DT>::from_bits((uint16_t)(szw[i >> 1] >> (16 * (i & 1))));
 #pragma unroll
           for (int h = 0; h < kMaxHeads; ++h)
-            if (h < gs) a.est_s2[((int64_t)g * kMaxHeads + h) * a.e_pad + pe] = sc[(int64_t)h * C + c] * RI_LOG2E;
-          if (a.estimated_ids) a.estimated_ids[(int64_t)g * a.E + pe] = c;
+            if (h < gs) a.est_s2[((int64_t)g * kMaxHeads + h) * a.e_pad + pe] = (&s4[h].x)[i] * RI_LOG2E;
+          if (a.estimated_ids) a.estimated_ids[(int64_t)g * a.E + pe] = lo + e + i;
         }
         ++pe;
       }
@@ -306,6 +339,8 @@ wave_select_kernel(SelectArgs a) {
       int rk = 0;
       for (int j = 0; j < a.P; ++j) rk += cand[j] > mine;   // distinct values: distinct ranks
       ranked[rk] = mine;
+      rcnt[rk] = cand_cnt[i];
+      roff[rk] = cand_off[i];
     }
     __syncthreads();
     int cnt[4], pages[4];
@@ -313,9 +348,7 @@ wave_select_kernel(SelectArgs a) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = tid * 4 + u;
-      const bool in = i < a.P;
-      const int cid = in ? 0xffff - (int)(ranked[i] & 0xffffu) : 0;
-      cnt[u] = in ? a.count[(int64_t)g * C + cid] : 0;
+      cnt[u] = i < a.P ? (int)rcnt[i] : 0;
       pages[u] = (cnt[u] + a.page - 1) / a.page;
       psum += (uint32_t)pages[u];
     }
@@ -347,6 +380,26 @@ wave_select_kernel(SelectArgs a) {
   cluster.sync();
 
   // ---- 6. all CTAs expand the kept clusters into row indices ----
+  // Lane l of a warp fetches the descriptor of the warp's l-th cluster from CTA 0; the cluster
+  // barrier is armed right after these remote reads and awaited only after the global stores, so
+  // its release never waits for them.
+  const int keep = *cluster.map_shared_rank(&s_keep, 0);
+  constexpr int kWarpsTotal = kSelectCluster * (kSelectThreads / 32);
+  const int my_i = rank * (kSelectThreads / 32) + warp + kWarpsTotal * lane;   // P <= 1024: at most 16 per warp
+  int d_off = 0, d_cnt = 0, d_start = 0;
+  if (my_i < keep) {
+    d_off = (int)cluster.map_shared_rank(roff, 0)[my_i];
+    d_cnt = (int)cluster.map_shared_rank(rcnt, 0)[my_i];
+    d_start = (int)cluster.map_shared_rank(rstart, 0)[my_i];
+  }
+  cluster_arrive();
+  const int n_mine = (keep - (rank * (kSelectThreads / 32) + warp) + kWarpsTotal - 1) / kWarpsTotal;
+  for (int l = 0; l < n_mine; ++l) {
+    const int off = __shfl_sync(0xffffffffu, d_off, l), cnt = __shfl_sync(0xffffffffu, d_cnt, l);
+    const int start = __shfl_sync(0xffffffffu, d_start, l);
+    for (int j = lane; j < cnt; j += 32)
+      if (start + j < a.max_rows) a.rows[(int64_t)g * a.max_rows + start + j] = off + j;
+  }
   for (int e = tid * 4; e < n_loc; e += kSelectThreads * 4) {   // the 16-bit distance keys (a view for tests)
     uint2 kw;
     kw.x = (uint32_t)keys[e] | ((uint32_t)keys[e + 1] << 16);
@@ -361,20 +414,7 @@ wave_select_kernel(SelectArgs a) {
     if (a.retrieved_ids)
       for (int i = tid; i < a.P; i += kSelectThreads) a.retrieved_ids[(int64_t)g * a.P + i] = 0xffff - (int)(ranked[i] & 0xffffu);
   }
-  {
-    const int keep = *cluster.map_shared_rank(&s_keep, 0);
-    const uint32_t* ranked0 = cluster.map_shared_rank(ranked, 0);
-    const uint32_t* rstart0 = cluster.map_shared_rank(rstart, 0);
-    for (int i = rank * (kSelectThreads / 32) + warp; i < keep; i += kSelectCluster * (kSelectThreads / 32)) {
-      const int cid = 0xffff - (int)(ranked0[i] & 0xffffu);
-      const int off = a.offset[(int64_t)g * (C + 1) + cid];
-      const int cnt = a.count[(int64_t)g * C + cid];
-      const int start = (int)rstart0[i];
-      for (int j = lane; j < cnt; j += 32)
-        if (start + j < a.max_rows) a.rows[(int64_t)g * a.max_rows + start + j] = off + j;
-    }
-  }
-  cluster.sync();   // CTA 0's shared memory must outlive the remote reads above
+  cluster_wait();   // CTA 0's shared memory must outlive the remote reads above
 }
 
 template <int DT>
@@ -401,7 +441,7 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   a.slice = ((p.n_centroids / 8 + kSelectCluster - 1) / kSelectCluster) * 8;
   a.p_pad = (int)ri_align_up(p.nprobe, 4);
   RI_REQUIRE(p.max_exact_rows < (1 << 20), "max_exact_rows=%d too large (limit 2^20 - 1)", p.max_exact_rows);
-  const size_t smem = ri_align16((size_t)a.slice * 2) + (size_t)a.p_pad * 12;
+  const size_t smem = ri_align16((size_t)a.slice * 2) + (size_t)a.p_pad * 28;
   if (smem > 48 * 1024)
     RI_CUDA_OK(cudaFuncSetAttribute(wave_select_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   wave_select_kernel<DT><<<dim3(kSelectCluster, p.groups), kSelectThreads, smem, s>>>(a);
