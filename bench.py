@@ -105,8 +105,8 @@ class Workload:
 
     def step_body(self):
         """One decode step of the hot path over all layers on the current stream: per layer the
-        reference's two calls (model_hub/LLM.py:116-117).  4 kernels of this library per layer:
-        steady append, scan, select, attend."""
+        reference's two calls (model_hub/LLM.py:116-117).  5 kernels of this library per layer:
+        steady append, scan, select, attend, combine."""
         for l in range(self.geo.layers):
             self.cache.decode_update_kv_cache(self.k_in[l], self.v_in[l], l)
             self.cache.compute(self.q_in[l], l, out=self.out[l])
@@ -135,7 +135,7 @@ class Workload:
             self.step_body()
 
     def launches_per_step(self):
-        return 4 * self.geo.layers
+        return 5 * self.geo.layers
 
     def static_len(self):
         return int(self.cache._per_device[str(self.device)]["static_len"].item())
