@@ -166,6 +166,39 @@ int64_t ri_kmeans_scratch_bytes(const ri_kmeans* p);
 int ri_kmeans_build(const ri_kmeans* p, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Gather/copy operators of the host tier (rows of 128 16-bit elements, pages of 8 rows).  Same
+ * argument order and meaning as the reference's pybind functions
+ * (library/retroinfer/retroinfer_kernels/src/gather_copy.cu:288-305), with tensors replaced by
+ * pointers and the stream made explicit.  Index arrays, and key_data2/value_data2 of the concat,
+ * may be pinned host memory (read through UVA), as in cache_hub/retroinfer_cache.py:124-173, :264-274.
+ * ------------------------------------------------------------------------------------------ */
+/* gather_copy.cu:25-96 — rows data_offsets[g, copy_start : copy_start+copy_num] of keys, values and
+ * the per-row 16-bit metadata go to the first copy_num rows of the buffers. */
+int ri_gather_copy_vectors(const void* key_data, void* key_buffer, const void* value_data, void* value_buffer,
+                           const void* src_metadata, void* dst_metadata, const int64_t* data_offsets,
+                           int32_t groups, int32_t data_length, int32_t buffer_length, int32_t index_size,
+                           int32_t copy_start, int32_t copy_num, void* stream);
+/* gather_copy.cu:100-212 — buffer rows = data1[:copy_vectors1] ++ listed pages of data2 (row-level
+ * start index) ++ listed pages of data3 (page-level index); valid_lengths[g] = rows written.
+ * data_length1/2 in rows, data_length3 in pages, buffer_length in rows. */
+int ri_gather_copy_and_concat(const void* key_data1, const void* key_data2, const void* key_data3,
+                              void* key_buffer, const void* value_data1, const void* value_data2,
+                              const void* value_data3, void* value_buffer, const int32_t* data_offsets2,
+                              const int32_t* data_copy_sizes2, const int32_t* buffer_offsets2,
+                              const int32_t* copy_chunks2, const int32_t* data_offsets3,
+                              const int32_t* data_copy_sizes3, const int32_t* buffer_offsets3,
+                              const int32_t* copy_chunks3, int32_t* valid_lengths, int32_t groups,
+                              int32_t data_length1, int64_t data_length2, int32_t data_length3,
+                              int32_t buffer_length, int32_t offset_length, int32_t copy_vectors1, void* stream);
+/* gather_copy.cu:216-283 — for each listed page: copy_sizes rows starting at s_copy_start + s_offsets of
+ * the source rows go to the first rows of destination page d_offsets. */
+int ri_gather_copy_and_scatter(const void* key_data, void* key_buffer, const void* value_data,
+                               void* value_buffer, const int32_t* s_offsets, const int32_t* copy_sizes,
+                               const int32_t* d_offsets, const int32_t* copy_chunks, int32_t groups,
+                               int32_t data_length, int32_t buffer_length, int32_t offset_length,
+                               int32_t s_copy_start, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Host-side wave buffer for the host tier (clusters whose KV stays in pinned host memory and is
  * cached page-wise on the GPU).  Replaces the descriptor/LRU part of `WaveBufferCPU`
  * (library/retroinfer/retroinfer_kernels/src/wave_buffer_cpu.cpp:261-816 and its pybind

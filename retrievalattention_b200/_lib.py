@@ -87,6 +87,13 @@ def _load() -> C.CDLL:
     lib.ri_wb_sync.argtypes = [C.c_void_p]
     lib.ri_wb_rows_used.restype = C.c_int64
     lib.ri_wb_rows_used.argtypes = [C.c_void_p, C.c_int32]
+    lib.ri_gather_copy_vectors.restype = C.c_int
+    lib.ri_gather_copy_vectors.argtypes = [C.c_void_p] * 7 + [C.c_int32] * 6 + [C.c_void_p]
+    lib.ri_gather_copy_and_concat.restype = C.c_int
+    lib.ri_gather_copy_and_concat.argtypes = ([C.c_void_p] * 17 + [C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                                                  C.c_int32, C.c_int32, C.c_void_p])
+    lib.ri_gather_copy_and_scatter.restype = C.c_int
+    lib.ri_gather_copy_and_scatter.argtypes = [C.c_void_p] * 8 + [C.c_int32] * 5 + [C.c_void_p]
     lib.ri_steady_append.restype = C.c_int
     lib.ri_steady_append.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_int32, C.c_void_p]
     return lib

@@ -46,7 +46,7 @@ struct AttendArgs {
   float* part_o;       // [slots, gs, 128]
   float* part_m;       // [slots, 8]
   float* part_l;       // [slots, 8]
-  int32_t* prefix;     // [G + 1] first step of every group (written by CTA 0, read by the combine)
+  int32_t* prefix;     // [G + 1] exact steps of all earlier groups (written by CTA 0, read by the combine)
   void* out;
   int64_t N;
   int G, C, gs, E, e_pad, e_steps, steady_stride, max_rows;
@@ -80,10 +80,11 @@ struct RowIds { int k[2]; int v[4]; };   // >= 0: row of the KV store / cluster 
 
 template <int DT>
 __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
+  ri_pdl_enter();
   extern __shared__ __align__(16) uint8_t dyn[];
   uint8_t* ring = dyn;
-  int* prefix = reinterpret_cast<int*>(dyn + kRingBytes);   // [G + 1] first step of each group
-  int* texact = prefix + a.G + 1;                            // [G] steady + retrieved rows of each group
+  int* px = reinterpret_cast<int*>(dyn + kRingBytes);       // [G + 1] exact steps of all earlier groups
+  int* texact = px + a.G + 1;                                // [G] steady + retrieved rows of each group
   __shared__ uint32_t scan_sums[4];
   __shared__ int s_carry;
 
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
     if (g < a.G) {
       const int te = static_len + a.n_exact[g];
       texact[g] = te;
-      steps = a.e_steps + (te + 15) / 16;
+      steps = (te + 15) / 16;
     }
     uint32_t inc = (uint32_t)steps;
 #pragma unroll
@@ -117,32 +118,45 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
       if (w < warp) base += scan_sums[w];
       tot += scan_sums[w];
     }
-    if (g < a.G) prefix[g] = (int)(base + inc) - steps;
+    if (g < a.G) px[g] = (int)(base + inc) - steps;
     __syncthreads();
     if (tid == 0) s_carry += (int)tot;
     __syncthreads();
   }
-  if (tid == 0) prefix[a.G] = s_carry;
+  if (tid == 0) px[a.G] = s_carry;
   __syncthreads();
-  const int total = prefix[a.G];
   if (blockIdx.x == 0)
-    for (int g = tid; g <= a.G; g += 128) a.prefix[g] = prefix[g];
-
-  // ---- this warp's contiguous range of steps (no CTA-wide barrier below this point) ----
-  const int n_warps = gridDim.x * 4;
-  const int per = (total + n_warps - 1) / n_warps;
-  const int wid = blockIdx.x * 4 + warp;
-  const int lo = min(total, wid * per), hi = min(total, lo + per);
-  if (lo >= hi) return;
-  int g_issue;
-  {   // group containing step lo: last g with prefix[g] <= lo
+    for (int g = tid; g <= a.G; g += 128) a.prefix[g] = px[g];
+  // An estimation step moves half the bytes of an exact step (no keys), so ranges are cut in cost
+  // units: 1 per estimation step, 2 per exact step.  A step belongs to the warp that holds its
+  // first unit.
+  const int es = a.e_steps;
+  auto step_start = [&](int g) { return g * es + px[g]; };        // first step of group g
+  auto unit_start = [&](int g) { return g * es + 2 * px[g]; };    // first cost unit of group g
+  auto group_of_unit = [&](int u) {                               // last g with unit_start(g) <= u
     int a0 = 0, b0 = a.G - 1;
     while (a0 < b0) {
       const int mid = (a0 + b0 + 1) >> 1;
-      if (prefix[mid] <= lo) a0 = mid; else b0 = mid - 1;
+      if (unit_start(mid) <= u) a0 = mid; else b0 = mid - 1;
     }
-    g_issue = a0;
-  }
+    return a0;
+  };
+  auto steps_before_unit = [&](int u) {                           // steps whose first unit is < u
+    const int g = group_of_unit(u);
+    const int uu = u - unit_start(g);
+    return step_start(g) + (uu < es ? uu : es + (uu - es + 1) / 2);
+  };
+  const int total_units = unit_start(a.G);
+
+  // ---- this warp's contiguous range of steps (no CTA-wide barrier below this point) ----
+  const int n_warps = gridDim.x * 4;
+  const int per = max(2, (total_units + n_warps - 1) / n_warps);   // >= 2: every range inside a group holds a step
+  const int wid = blockIdx.x * 4 + warp;
+  const int lu = min(total_units, wid * per), hu = min(total_units, lu + per);
+  const int lo = steps_before_unit(lu), hi = steps_before_unit(hu);
+  if (lo >= hi) return;
+  int g_issue = group_of_unit(lu);
+  while (lo >= step_start(g_issue + 1)) ++g_issue;   // lu may sit in the middle of the previous group's last step
   int g_cur = g_issue;
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStages * kStageBytes + lane * 16;
   const uint8_t* my_ring_ptr = ring + warp * kStages * kStageBytes + lane * 16;
@@ -150,7 +164,7 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
   // ids of the rows this lane touches in step s of group g
   auto load_ids = [&](int s, int g) {
     RowIds id;
-    const int j = s - prefix[g];
+    const int j = s - step_start(g);
     const bool est = j < a.e_steps;
     const int base = (est ? j : j - a.e_steps) * 16;
     const int last = (est ? a.E : texact[g]) - 1;
@@ -172,7 +186,7 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
   // start the copies of step s (group g) into ring stage `stage`
   auto issue = [&](int s, int g, int stage, const RowIds& id) {
     const uint32_t dst = my_ring + stage * kStageBytes;
-    const int j = s - prefix[g];
+    const int j = s - step_start(g);
     if (j < a.e_steps) {
       // pieces 0/1: this lane's scores and weights of the step; pieces 8..15: value-sum rows
       const int i0 = j * 16 + 2 * t;
@@ -249,7 +263,7 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
       issue(s_issue, g_issue, st, nid);
       ++s_issue;
       if (s_issue < hi) {
-        while (s_issue >= prefix[g_issue + 1]) ++g_issue;
+        while (s_issue >= step_start(g_issue + 1)) ++g_issue;
         nid = load_ids(s_issue, g_issue);
       }
     }
@@ -260,14 +274,14 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
   int stage = 0;
 #pragma unroll 1
   for (int s = lo; s < hi; ++s) {
-    if (s >= prefix[g_cur + 1]) {          // entering the next group: hand over what was accumulated
+    if (s >= step_start(g_cur + 1)) {          // entering the next group: hand over what was accumulated
       flush(g_cur);
-      while (s >= prefix[g_cur + 1]) ++g_cur;
+      while (s >= step_start(g_cur + 1)) ++g_cur;
       reset(g_cur);
     }
     cp_async_wait<kStages - 1>();           // the group of step s has landed (lane-private slots: no barrier)
     const uint8_t* src = my_ring_ptr + stage * kStageBytes;
-    const int j = s - prefix[g_cur];
+    const int j = s - step_start(g_cur);
     const bool is_est = j < a.e_steps;
     const int base = (is_est ? j : j - a.e_steps) * 16;
     const int rows_end = is_est ? a.E : texact[g_cur];
@@ -337,7 +351,7 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
       issue(s_issue, g_issue, stage, nid);
       ++s_issue;
       if (s_issue < hi) {
-        while (s_issue >= prefix[g_issue + 1]) ++g_issue;
+        while (s_issue >= step_start(g_issue + 1)) ++g_issue;
         nid = load_ids(s_issue, g_issue);
       }
     }
@@ -353,19 +367,25 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
 template <int DT>
 __global__ void __launch_bounds__(128) wave_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
                                                            const float* __restrict__ part_l, const int32_t* __restrict__ prefix,
-                                                           void* out, int G, int gs, int n_warps) {
+                                                           void* out, int G, int gs, int n_warps, int e_steps) {
+  ri_pdl_enter();
   extern __shared__ float factor[];          // [slots of this group]
   __shared__ float red[4];
   __shared__ float s_M, s_L;
   const int h = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int total = prefix[G], p0 = prefix[g], p1 = prefix[g + 1];
-  const int per = (total + n_warps - 1) / n_warps;
+  // same cost-unit arithmetic as the attend kernel (prefix[] = exact steps of all earlier groups)
+  const int total_units = G * e_steps + 2 * prefix[G];
+  const int per = max(2, (total_units + n_warps - 1) / n_warps);
+  const int u0 = g * e_steps + 2 * prefix[g];                       // first unit of the group's first step
+  const int x_steps = prefix[g + 1] - prefix[g];
+  const int n_steps = e_steps + x_steps;
   uint16_t* o = reinterpret_cast<uint16_t*>(out) + ((int64_t)g * gs + h) * RI_HEAD_DIM;
-  if (p1 <= p0) {                              // a group without rows: zero output
+  if (n_steps <= 0) {                          // a group without rows: zero output
     o[tid] = 0;
     return;
   }
-  const int w0 = p0 / per, n = (p1 - 1) / per - w0 + 1;
+  const int u_last = x_steps > 0 ? u0 + e_steps + 2 * (x_steps - 1) : u0 + e_steps - 1;   // first unit of its last step
+  const int w0 = u0 / per, n = u_last / per - w0 + 1;
   const int64_t slot0 = (int64_t)w0 + g;
   float M = -INFINITY;
   for (int c = tid; c < n; c += 128) M = fmaxf(M, part_m[(slot0 + c) * kMaxHeads + h]);
@@ -455,11 +475,10 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   const int ctas = attend_ctas();
   const int smem = kRingBytes + (2 * p.groups + 1) * 4;
   RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  wave_attend_kernel<DT><<<ctas, 128, smem, s>>>(a);
-  RI_LAUNCH_OK("wave_attend_kernel");
-  wave_combine_kernel<DT><<<dim3(p.group_size, p.groups), 128, (size_t)ctas * 4 * sizeof(float), s>>>(
-      a.part_o, a.part_m, a.part_l, a.prefix, p.d_out, p.groups, p.group_size, ctas * 4);
-  RI_LAUNCH_OK("wave_combine_kernel");
+  RI_CUDA_OK(ri_launch_pdl_id(2, wave_attend_kernel<DT>, dim3(ctas), dim3(128), (size_t)smem, s, a));
+  RI_CUDA_OK(ri_launch_pdl_id(3, wave_combine_kernel<DT>, dim3(p.group_size, p.groups), dim3(128),
+                           (size_t)ctas * 4 * sizeof(float), s, (const float*)a.part_o, (const float*)a.part_m,
+                           (const float*)a.part_l, (const int32_t*)a.prefix, p.d_out, p.groups, p.group_size, ctas * 4, a.e_steps));
   return RI_OK;
 }
 

@@ -40,6 +40,7 @@ int validate(const ri_wave_layer* p) {
 
 __global__ void steady_append_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, uint4* sk, uint4* sv,
                                      const int32_t* __restrict__ pos, int groups, int stride) {
+  ri_pdl_enter();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece each
   if (i >= groups * 16) return;
   const int g = i >> 4, c = i & 15;
@@ -105,9 +106,9 @@ extern "C" int ri_steady_append(const void* d_k, const void* d_v, void* d_steady
   RI_REQUIRE(d_k && d_v && d_steady_keys && d_steady_values && d_position, "ri_steady_append: null pointer");
   RI_REQUIRE(groups > 0 && steady_stride > 0, "ri_steady_append: bad sizes");
   const int n = groups * 16;
-  steady_append_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(d_k), static_cast<const uint4*>(d_v), static_cast<uint4*>(d_steady_keys),
-      static_cast<uint4*>(d_steady_values), d_position, groups, steady_stride);
-  RI_LAUNCH_OK("steady_append_kernel");
+  RI_CUDA_OK(ri_launch_pdl_id(4, steady_append_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                           static_cast<const uint4*>(d_k), static_cast<const uint4*>(d_v),
+                           static_cast<uint4*>(d_steady_keys), static_cast<uint4*>(d_steady_values), d_position, groups,
+                           steady_stride));
   return RI_OK;
 }

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(128) wave_scan_kernel(const uint4* __restrict_
                                                         float* __restrict__ scores, float* __restrict__ tile_max,
                                                         float* __restrict__ tile_sum, int C, int gs, int n_tiles,
                                                         float alpha) {
+  ri_pdl_enter();
   const int g = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, t = lane & 3;
@@ -91,11 +92,10 @@ template <int DT>
 int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   uint8_t* sc = static_cast<uint8_t*>(p.d_scratch);
   dim3 grid(L.n_tiles, p.groups);
-  wave_scan_kernel<DT><<<grid, 128, 0, s>>>(
-      static_cast<const uint4*>(p.d_q), static_cast<const uint4*>(p.d_centroids), reinterpret_cast<float*>(sc + L.scores),
-      reinterpret_cast<float*>(sc + L.tile_max), reinterpret_cast<float*>(sc + L.tile_sum), p.n_centroids, p.group_size,
-      L.n_tiles, 0.08838834764831845f);
-  RI_LAUNCH_OK("wave_scan_kernel");
+  RI_CUDA_OK(ri_launch_pdl_id(0, wave_scan_kernel<DT>, grid, dim3(128), 0, s, static_cast<const uint4*>(p.d_q),
+                           static_cast<const uint4*>(p.d_centroids), reinterpret_cast<float*>(sc + L.scores),
+                           reinterpret_cast<float*>(sc + L.tile_max), reinterpret_cast<float*>(sc + L.tile_sum),
+                           p.n_centroids, p.group_size, L.n_tiles, 0.08838834764831845f));
   return RI_OK;
 }
 

@@ -117,6 +117,7 @@ __device__ __forceinline__ void find_bins(const int* ga, const int* la, int ka, 
 template <int DT>
 __global__ void __cluster_dims__(kSelectCluster, 1, 1) __launch_bounds__(kSelectThreads)
 wave_select_kernel(SelectArgs a) {
+  ri_pdl_enter();
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t dyn[];
   uint16_t* keys = reinterpret_cast<uint16_t*>(dyn);                                   // [slice]
@@ -444,8 +445,7 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   const size_t smem = ri_align16((size_t)a.slice * 2) + (size_t)a.p_pad * 28;
   if (smem > 48 * 1024)
     RI_CUDA_OK(cudaFuncSetAttribute(wave_select_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  wave_select_kernel<DT><<<dim3(kSelectCluster, p.groups), kSelectThreads, smem, s>>>(a);
-  RI_LAUNCH_OK("wave_select_kernel");
+  RI_CUDA_OK(ri_launch_pdl_id(1, wave_select_kernel<DT>, dim3(kSelectCluster, p.groups), dim3(kSelectThreads), smem, s, a));
   return RI_OK;
 }
 

@@ -79,3 +79,45 @@ class WaveBufferCPU:
 
     def sync(self):
         _lib.check(_lib.lib.ri_wb_sync(self._h), "ri_wb_sync")
+
+
+def _p(t: torch.Tensor) -> int:
+    """Address of a contiguous CUDA or pinned-host tensor."""
+    assert t.is_contiguous(), "operator arguments must be contiguous"
+    assert t.is_cuda or t.is_pinned(), "host tensors must be pinned (they are read through UVA)"
+    return t.data_ptr()
+
+
+def gather_copy_vectors(key_data, key_buffer, value_data, value_buffer, src_metadata, dst_metadata, data_offsets,
+                        groups, data_length, buffer_length, index_size, copy_start, copy_num):
+    """gather_copy.cu:25-96 (same argument list)."""
+    assert key_data.element_size() == 2 and key_data.shape[-1] == 128 and data_offsets.dtype == torch.int64
+    _lib.check(_lib.lib.ri_gather_copy_vectors(
+        _p(key_data), _p(key_buffer), _p(value_data), _p(value_buffer), _p(src_metadata), _p(dst_metadata),
+        _p(data_offsets), groups, data_length, buffer_length, index_size, copy_start, copy_num, _lib.current_stream()),
+        "ri_gather_copy_vectors")
+
+
+def gather_copy_and_concat(key_data1, key_data2, key_data3, key_buffer, value_data1, value_data2, value_data3,
+                           value_buffer, data_offsets2, data_copy_sizes2, buffer_offsets2, copy_chunks2, data_offsets3,
+                           data_copy_sizes3, buffer_offsets3, copy_chunks3, valid_lengths, groups, data_length1,
+                           data_length2, data_length3, buffer_length, offset_length, copy_vectors1):
+    """gather_copy.cu:100-212 (same argument list)."""
+    assert key_data1.element_size() == 2 and key_data1.shape[-1] == 128
+    idx = (data_offsets2, data_copy_sizes2, buffer_offsets2, copy_chunks2, data_offsets3, data_copy_sizes3,
+           buffer_offsets3, copy_chunks3, valid_lengths)
+    assert all(t.dtype == torch.int32 for t in idx)
+    _lib.check(_lib.lib.ri_gather_copy_and_concat(
+        _p(key_data1), _p(key_data2), _p(key_data3), _p(key_buffer), _p(value_data1), _p(value_data2), _p(value_data3),
+        _p(value_buffer), *[_p(t) for t in idx], groups, data_length1, data_length2, data_length3, buffer_length,
+        offset_length, copy_vectors1, _lib.current_stream()), "ri_gather_copy_and_concat")
+
+
+def gather_copy_and_scatter(key_data, key_buffer, value_data, value_buffer, s_offsets, copy_sizes, d_offsets,
+                            copy_chunks, groups, data_length, buffer_length, offset_length, s_copy_start):
+    """gather_copy.cu:216-283 (same argument list)."""
+    assert all(t.dtype == torch.int32 for t in (s_offsets, copy_sizes, d_offsets, copy_chunks))
+    _lib.check(_lib.lib.ri_gather_copy_and_scatter(
+        _p(key_data), _p(key_buffer), _p(value_data), _p(value_buffer), _p(s_offsets), _p(copy_sizes), _p(d_offsets),
+        _p(copy_chunks), groups, data_length, buffer_length, offset_length, s_copy_start, _lib.current_stream()),
+        "ri_gather_copy_and_scatter")
