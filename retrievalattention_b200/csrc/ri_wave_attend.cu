@@ -27,7 +27,11 @@
 namespace ri_wave {
 namespace {
 
-constexpr int kStages = 3;
+#ifndef RI_ATTEND_STAGES
+#define RI_ATTEND_STAGES 3
+#endif
+constexpr int kStages = RI_ATTEND_STAGES;
+constexpr int kCtasPerSm = RI_ATTEND_STAGES == 2 ? 3 : 2;
 constexpr int kStageBytes = 16 * 32 * 16;       // 16 pieces x 32 lanes x 16 bytes = 8 KB per warp and stage
 constexpr int kRingBytes = 4 * kStages * kStageBytes;
 
@@ -80,7 +84,7 @@ __device__ __forceinline__ void pv_step(float (&acc)[8][4], const uint4 (&v)[4][
 struct RowIds { int k[2]; int v[4]; };   // >= 0: row of the KV store / cluster id; < 0: steady row -1-id
 
 template <int DT>
-__global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
+__global__ void __launch_bounds__(128, kCtasPerSm) wave_attend_kernel(AttendArgs a) {
   ri_pdl_enter();
   extern __shared__ __align__(16) uint8_t ring[];
   __shared__ float sm_m[4][kMaxHeads], sm_l[4][kMaxHeads];
@@ -213,15 +217,16 @@ __global__ void __launch_bounds__(128, 2) wave_attend_kernel(AttendArgs a) {
       } else {
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
-          float c[4] = {0.f, 0.f, 0.f, 0.f};
+          // two independent accumulation chains of four MMAs each instead of one of eight
+          float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint4 kb = *reinterpret_cast<const uint4*>(src + (4 * jj + kk) * 512);
             Elem<DT>::mma16816(c, qa[kk].x, 0u, qa[kk].y, 0u, kb.x, kb.y);
-            Elem<DT>::mma16816(c, qa[kk].z, 0u, qa[kk].w, 0u, kb.z, kb.w);
+            Elem<DT>::mma16816(c2, qa[kk].z, 0u, qa[kk].w, 0u, kb.z, kb.w);
           }
-          s2[jj][0] = c[0] * a.scale2;
-          s2[jj][1] = c[1] * a.scale2;
+          s2[jj][0] = (c[0] + c2[0]) * a.scale2;
+          s2[jj][1] = (c[1] + c2[1]) * a.scale2;
         }
       }
 #pragma unroll
@@ -379,7 +384,7 @@ int attend_ctas() {
   if (cached[dev] == 0) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    cached[dev] = sms * 2 < kAttendMaxCtas ? sms * 2 : kAttendMaxCtas;
+    cached[dev] = sms * kCtasPerSm < kAttendMaxCtas ? sms * kCtasPerSm : kAttendMaxCtas;
   }
   return cached[dev];
 }
