@@ -94,9 +94,10 @@ constexpr float RI_LOG2E = 1.4426950408889634f;
 // visible.  All global reads and writes of a kernel come after this call, so the chain keeps
 // plain stream-order semantics while the launch latency between dependent kernels is hidden.
 // Launched without the attribute (or after a non-kernel operation) both instructions are no-ops.
-// Measured on B200: worth a few tenths of a microsecond per launch for scan, select and attend
-// (ids 0-2, on by default); early-resident combine CTAs slowed the attend kernel down, so the
-// combine and the steady append (ids 3, 4) are launched in plain stream order.
+// Measured on B200: worth a few tenths of a microsecond per launch for scan and select (ids 0, 1,
+// on by default).  The attend kernel (id 2: 8-CTA clusters with ~100 KB of shared memory each)
+// got slower when its CTAs became resident early, so it and the steady append (id 4) are
+// launched in plain stream order.
 __device__ __forceinline__ void ri_pdl_enter() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -113,7 +114,7 @@ inline cudaError_t ri_launch_pdl_id(int id, void (*kernel)(KArgs...), dim3 grid,
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  static const int mask = getenv("RI_PDL_MASK") ? atoi(getenv("RI_PDL_MASK")) : 7;   // per-kernel switch (debugging)
+  static const int mask = getenv("RI_PDL_MASK") ? atoi(getenv("RI_PDL_MASK")) : 3;   // per-kernel switch (debugging)
   cfg.attrs = attr;
   cfg.numAttrs = (mask >> id) & 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);

@@ -5,15 +5,15 @@
 // (reference: the two weighted_flash_decoding calls, cache_hub/retroinfer_cache.py:611-617 and
 // :666-674, with gather_copy_vectors :601-605 and gather_copy_and_concat :642-648 in between).
 //
-// Work decomposition: the CTAs of a fixed, SM-filling grid (2 per SM, 4 warps each) are dealt out
-// evenly to the groups.  Inside a group the 16-row steps (ceil(E/16) estimation steps, then
+// Work decomposition: a fixed, SM-filling grid of 8-CTA clusters (2 CTAs per SM, 4 warps each); a
+// cluster works on one group at a time.  Inside a group the 16-row steps (ceil(E/16) estimation steps, then
 // ceil((steady + retrieved rows)/16) exact steps) are cut into equal-cost contiguous ranges, one
 // per warp (an exact step moves twice the bytes of an estimation step).  A warp streams its steps
 // through a lane-private three-stage cp.async ring in shared memory (256 bytes per lane and step;
 // the row ids of the next step to issue are prefetched into registers) and keeps running
-// (max, sum, O).  The four warps of a CTA merge in shared memory into one partial result; the last
-// CTA of a group to finish (atomic ticket) merges the group's partials by log-sum-exp and writes
-// the output.
+// (max, sum, O).  The four warps of a CTA merge in shared memory into one partial result; the 8 CTAs
+// of a group form a thread-block cluster and merge their partials by log-sum-exp through
+// distributed shared memory, each CTA finishing one eighth of the output values.
 //
 // Tensor-core use: m16n8k16 MMA.  QK^T has the GQA group in M and 8 rows in N, with the same
 // channel permutation on both operands as in the scan.  PV is computed transposed (16 channels in
@@ -22,7 +22,11 @@
 // takes channel word x of those pieces: low halves are MMA rows r, high halves rows r+8, so tile x,
 // row r is channel ch(x) = (x<4 ? 8r+2x : 64+8r+2(x-4)) and row r+8 is ch(x)+1.  The probabilities
 // come straight from the QK^T accumulators as the B fragment.
+#include <cooperative_groups.h>
+
 #include "ri_wave_internal.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace ri_wave {
 namespace {
@@ -32,6 +36,12 @@ namespace {
 #endif
 constexpr int kStages = RI_ATTEND_STAGES;
 constexpr int kCtasPerSm = RI_ATTEND_STAGES == 2 ? 3 : 2;
+constexpr int kAttendCluster = 8;   // CTAs per group
+#ifndef RI_COST_EST
+#define RI_COST_EST 2
+#define RI_COST_EXACT 3
+#endif
+constexpr int kCostEst = RI_COST_EST, kCostExact = RI_COST_EXACT;   // relative cost of a step (bytes moved)
 constexpr int kStageBytes = 16 * 32 * 16;       // 16 pieces x 32 lanes x 16 bytes = 8 KB per warp and stage
 constexpr int kRingBytes = 4 * kStages * kStageBytes;
 
@@ -48,10 +58,6 @@ struct AttendArgs {
   const int32_t* est_ids;
   const float* est_w;
   const float* est_s2;
-  float* part_o;       // [slots, gs, 128]
-  float* part_m;       // [slots, 8]
-  float* part_l;       // [slots, 8]
-  uint32_t* counters;  // [G] arrival tickets (zero between launches)
   void* out;
   int64_t N;
   int G, C, gs, E, e_pad, e_steps, steady_stride, max_rows;
@@ -84,32 +90,35 @@ __device__ __forceinline__ void pv_step(float (&acc)[8][4], const uint4 (&v)[4][
 struct RowIds { int k[2]; int v[4]; };   // >= 0: row of the KV store / cluster id; < 0: steady row -1-id
 
 template <int DT>
-__global__ void __launch_bounds__(128, kCtasPerSm) wave_attend_kernel(AttendArgs a) {
+__global__ void __cluster_dims__(kAttendCluster, 1, 1) __launch_bounds__(128, kCtasPerSm) wave_attend_kernel(AttendArgs a) {
   ri_pdl_enter();
   extern __shared__ __align__(16) uint8_t ring[];
   __shared__ float sm_m[4][kMaxHeads], sm_l[4][kMaxHeads];
-  __shared__ int s_last;
+  __shared__ float cta_o[kMaxHeads][RI_HEAD_DIM], cta_m[kMaxHeads], cta_l[kMaxHeads];   // this CTA's partial result
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
   const int gs = a.gs, es = a.e_steps;
   const int static_len = *a.static_len;
-  const int cpg = max(1, (int)gridDim.x / a.G);          // CTAs per group
-  const int groups_per_pass = (int)gridDim.x / cpg;
-  if ((int)blockIdx.x >= groups_per_pass * cpg) return;  // left-over CTAs when the grid does not divide evenly
-  const int cl = (int)blockIdx.x % cpg;
+  cg::cluster_group cluster = cg::this_cluster();
+  constexpr int cpg = kAttendCluster;                    // CTAs per group
+  const int groups_per_pass = (int)gridDim.x / cpg;      // clusters in the grid
+  const int cl = (int)cluster.block_rank();
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStages * kStageBytes + lane * 16;
   const uint8_t* my_ring_ptr = ring + warp * kStages * kStageBytes + lane * 16;
   auto warp_o = [&](int w) { return reinterpret_cast<float*>(ring + w * kStages * kStageBytes); };
 
-  for (int g = (int)blockIdx.x / cpg; g < a.G; g += groups_per_pass) {
+  for (int g = (int)blockIdx.x / cpg; g < a.G; g += groups_per_pass) {   // uniform over the cluster
     const int te = static_len + a.n_exact[g];           // steady + retrieved rows
     const int xs = (te + 15) / 16;
-    // cost units: 1 per estimation step, 2 per exact step; a step belongs to the warp holding its first unit
-    const int units = es + 2 * xs;
+    // cost units: kCostEst per estimation step, kCostExact per exact step; a step belongs to the warp holding
+    // its first unit (an estimation step moves half the bytes but costs about two thirds of the time, measured)
+    const int units = kCostEst * es + kCostExact * xs;
     const int n_w = cpg * 4, wl = cl * 4 + warp;
-    const int per = max(2, (units + n_w - 1) / n_w);
-    auto steps_before_unit = [&](int u) { return u < es ? u : es + (u - es + 1) / 2; };
+    const int per = max(kCostExact, (units + n_w - 1) / n_w);
+    auto steps_before_unit = [&](int u) {
+      return u < kCostEst * es ? (u + kCostEst - 1) / kCostEst : es + (u - kCostEst * es + kCostExact - 1) / kCostExact;
+    };
     const int lu = min(units, wl * per), hu = min(units, lu + per);
     const int lo = steps_before_unit(lu), hi = steps_before_unit(hu);
 
@@ -293,7 +302,6 @@ __global__ void __launch_bounds__(128, kCtasPerSm) wave_attend_kernel(AttendArgs
       }
     }
     __syncthreads();
-    const int64_t slot = (int64_t)g * cpg + cl;
     for (int h = 0; h < gs; ++h) {
       const float M = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
       const float Ms = M == -INFINITY ? 0.f : M;
@@ -304,76 +312,36 @@ __global__ void __launch_bounds__(128, kCtasPerSm) wave_attend_kernel(AttendArgs
         L += sm_l[wi][h] * f;
         O += warp_o(wi)[h * RI_HEAD_DIM + tid] * f;
       }
-      a.part_o[(slot * gs + h) * RI_HEAD_DIM + tid] = O;
-      if (tid == 0) { a.part_m[slot * kMaxHeads + h] = M; a.part_l[slot * kMaxHeads + h] = L; }
+      cta_o[h][tid] = O;
+      if (tid == 0) { cta_m[h] = M; cta_l[h] = L; }
     }
+    cluster.sync();
 
-    // ---- the last CTA of the group to arrive combines its cpg partial results ----
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const uint32_t ticket = atomicAdd(&a.counters[g], 1u);
-      s_last = ticket == (uint32_t)(cpg - 1);
+    // ---- merge the 8 partial results of the group through distributed shared memory: this CTA
+    //      finishes values [cl * gs*16, (cl+1) * gs*16) of the gs*128 outputs ----
+    if (tid < gs * 16) {
+      const int v = cl * gs * 16 + tid, h = v >> 7, ch = v & 127;
+      float mc[cpg], lc[cpg], oc[cpg];
+#pragma unroll
+      for (int c = 0; c < cpg; ++c) {
+        mc[c] = cluster.map_shared_rank(cta_m, c)[h];
+        lc[c] = cluster.map_shared_rank(cta_l, c)[h];
+        oc[c] = cluster.map_shared_rank(&cta_o[0][0], c)[h * RI_HEAD_DIM + ch];
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < cpg; ++c) M = fmaxf(M, mc[c]);
+      const float Ms = M == -INFINITY ? 0.f : M;
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int c = 0; c < cpg; ++c) {
+        const float f = exp2f(mc[c] - Ms);
+        L += lc[c] * f;
+        O += oc[c] * f;
+      }
+      reinterpret_cast<uint16_t*>(a.out)[((int64_t)g * gs + h) * RI_HEAD_DIM + ch] = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
     }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      const int64_t sbase = (int64_t)g * cpg;
-      // tables (cpg <= 512 rows of 8 heads) reuse the ring; all loads below are independent
-      float* tf = reinterpret_cast<float*>(ring);      // running max, then the rescale factor 2^(m - M)
-      float* tl = tf + kAttendMaxCtas * kMaxHeads;     // denominators
-      for (int i = tid; i < cpg * kMaxHeads; i += 128) {
-        tf[i] = __ldcg(a.part_m + sbase * kMaxHeads + i);
-        tl[i] = __ldcg(a.part_l + sbase * kMaxHeads + i);
-      }
-      __syncthreads();
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {                 // warp w reduces heads 2w and 2w+1
-        const int h = warp * 2 + hh;
-        float M = -INFINITY;
-        for (int c = lane; c < cpg; c += 32) M = fmaxf(M, tf[c * kMaxHeads + h]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        const float Ms = M == -INFINITY ? 0.f : M;
-        float L = 0.f;
-        for (int c = lane; c < cpg; c += 32) {
-          const float f = exp2f(tf[c * kMaxHeads + h] - Ms);
-          tf[c * kMaxHeads + h] = f;
-          L += tl[c * kMaxHeads + h] * f;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-        if (lane == 0) sm_l[0][h] = L;
-      }
-      __syncthreads();
-      const int dq = tid >> 2, c4 = tid & 3;           // 4 channels per thread, partials split 4 ways
-      for (int h = 0; h < gs; ++h) {
-        float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int c = c4; c < cpg; c += 4) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_o + ((sbase + c) * gs + h) * RI_HEAD_DIM) + dq);
-          const float f = tf[c * kMaxHeads + h];
-          o4.x += v.x * f; o4.y += v.y * f; o4.z += v.z * f; o4.w += v.w * f;
-        }
-#pragma unroll
-        for (int o = 1; o <= 2; o <<= 1) {
-          o4.x += __shfl_xor_sync(0xffffffffu, o4.x, o);
-          o4.y += __shfl_xor_sync(0xffffffffu, o4.y, o);
-          o4.z += __shfl_xor_sync(0xffffffffu, o4.z, o);
-          o4.w += __shfl_xor_sync(0xffffffffu, o4.w, o);
-        }
-        if (c4 == 0) {
-          const float L = sm_l[0][h];
-          const float inv = L > 0.f ? 1.0f / L : 0.f;
-          uint2 o2;
-          o2.x = Elem<DT>::pack2(o4.x * inv, o4.y * inv);
-          o2.y = Elem<DT>::pack2(o4.z * inv, o4.w * inv);
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.out) + ((int64_t)g * gs + h) * RI_HEAD_DIM + 4 * dq) = o2;
-        }
-      }
-      if (tid == 0) a.counters[g] = 0u;   // leave the scratch reusable
-    }
-    __syncthreads();                       // the ring is reused by the next group of this CTA
+    cluster.sync();                        // remote reads done: the partials and the ring may be reused
   }
 }
 
@@ -405,17 +373,14 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   a.est_ids = reinterpret_cast<const int32_t*>(sc + L.est_ids);
   a.est_w = reinterpret_cast<const float*>(sc + L.est_w);
   a.est_s2 = reinterpret_cast<const float*>(sc + L.est_s2);
-  a.part_o = reinterpret_cast<float*>(sc + L.part_o);
-  a.part_m = reinterpret_cast<float*>(sc + L.part_m);
-  a.part_l = reinterpret_cast<float*>(sc + L.part_l);
-  a.counters = reinterpret_cast<uint32_t*>(sc + L.counters);
   a.out = p.d_out;
   a.N = p.tokens_per_group;
   a.G = p.groups; a.C = p.n_centroids; a.gs = p.group_size; a.E = p.n_estimate; a.e_pad = L.e_pad;
   a.e_steps = (p.n_estimate + 15) / 16;
   a.steady_stride = p.steady_stride; a.max_rows = p.max_exact_rows;
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
-  const int ctas = attend_ctas();
+  const int clusters = min(p.groups, max(1, attend_ctas() / kAttendCluster));
+  const int ctas = clusters * kAttendCluster;
   RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
   RI_CUDA_OK(ri_launch_pdl_id(2, wave_attend_kernel<DT>, dim3(ctas), dim3(128), (size_t)kRingBytes, s, a));
   return RI_OK;

@@ -14,20 +14,18 @@ constexpr int kAttendMaxCtas = 512; // persistent attend CTAs (2 per SM) the scr
 constexpr int kAttendMaxGroups = 4096;
 
 struct Layout {
-  int64_t counters, scores, tile_max, tile_sum, dist_keys, est_ids, est_w, est_s2, rows, n_exact, part_o,
-      part_m, part_l, total;
-  int e_pad, n_slots, n_tiles;
+  int64_t counters, scores, tile_max, tile_sum, dist_keys, est_ids, est_w, est_s2, rows, n_exact, total;
+  int e_pad, n_tiles;
 };
 
 inline Layout make_layout(const ri_wave_layer& p) {
   Layout L;
   const int64_t G = p.groups;
   L.e_pad = (int)ri_align_up(p.n_estimate > 0 ? p.n_estimate : 1, 16);
-  L.n_slots = p.groups + kAttendMaxCtas;   // one partial result per (attend CTA, group) pair
   L.n_tiles = (p.n_centroids + kScanTile - 1) / kScanTile;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { int64_t o = off; off = ri_align_up(off + bytes, 256); return o; };
-  L.counters = take(G * 4);   // first: the only region that must start zeroed
+  L.counters = take(G * 4);   // reserved word per group at the front (callers zero it once; unused by the kernels)
   L.scores = take(G * p.group_size * (int64_t)p.n_centroids * 4);
   L.tile_max = take(G * kMaxHeads * (int64_t)L.n_tiles * 4);
   L.tile_sum = take(G * kMaxHeads * (int64_t)L.n_tiles * 4);
@@ -37,9 +35,6 @@ inline Layout make_layout(const ri_wave_layer& p) {
   L.est_s2 = take(G * kMaxHeads * (int64_t)L.e_pad * 4);
   L.rows = take(G * (int64_t)p.max_exact_rows * 4);
   L.n_exact = take(G * 4);
-  L.part_o = take(L.n_slots * (int64_t)p.group_size * RI_HEAD_DIM * 4);
-  L.part_m = take((int64_t)L.n_slots * kMaxHeads * 4);
-  L.part_l = take((int64_t)L.n_slots * kMaxHeads * 4);
   L.total = off;
   return L;
 }
