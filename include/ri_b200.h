@@ -107,6 +107,15 @@ int ri_wave_scan(const ri_wave_layer* p, void* stream);    /* q.C^T scores -> sc
 int ri_wave_select(const ri_wave_layer* p, void* stream);  /* softmax, group sum, top-k split */
 int ri_wave_attend(const ri_wave_layer* p, void* stream);  /* weighted split-K flash decoding */
 
+/* Host tier: the attend stage over an execution buffer assembled by ri_gather_copy_and_concat
+ * (steady zone ++ missed pages from the host list ++ hit pages from the GPU page cache).  The
+ * estimation part is as in ri_wave_attend (it uses what ri_wave_select left in the scratch); the
+ * exact rows are the first d_valid_lengths[g] rows of d_exec_keys/values [G, exec_stride, 128].
+ * Replaces the merging weighted_flash_decoding call on the reference's execution buffer
+ * (cache_hub/retroinfer_cache.py:666-674). */
+int ri_wave_attend_buffer(const ri_wave_layer* p, const void* d_exec_keys, const void* d_exec_values,
+                          int32_t exec_stride, const int32_t* d_valid_lengths, void* stream);
+
 /* Views into the scratch (device pointers valid after ri_wave_select), for tests. */
 typedef struct ri_wave_views {
   const float* d_scores;        /* [G, gs, C] alpha*q.c in fp32 */

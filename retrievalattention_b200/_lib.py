@@ -65,6 +65,8 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]
+    lib.ri_wave_attend_buffer.restype = C.c_int
+    lib.ri_wave_attend_buffer.argtypes = [C.POINTER(WaveLayer), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.ri_wave_scratch_views.restype = C.c_int
     lib.ri_wave_scratch_views.argtypes = [C.POINTER(WaveLayer), C.POINTER(WaveViews)]
     lib.ri_kmeans_scratch_bytes.restype = C.c_int64

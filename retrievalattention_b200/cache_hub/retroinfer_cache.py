@@ -7,9 +7,20 @@ What is the same: constructor arguments, ``prefill_update_kv_cache`` / ``sync`` 
 parameters and the page budget ``buffer_size`` (:107-111).
 
 What differs underneath: the index is built on the GPU by ``ri_kmeans_build`` (no pinned-host
-offload, no CPU re-layout), and one decode layer is one ``ri_wave_decode_layer`` call with no host
-synchronisation.  ``core``, ``cache_cluster_num`` and ``use_cluster_estimation`` are accepted for
-compatibility; the GPU page cache they size does not exist here because nothing lives on the host.
+offload, no CPU re-layout).  Two storage tiers:
+
+* default (``kv_on_host=False``): the whole cluster-contiguous KV stays in HBM and one decode layer is
+  one ``ri_wave_decode_layer`` call with no host synchronisation.  ``core`` and ``cache_cluster_num``
+  are accepted but unused — nothing lives on the host, so there is no page cache to size.
+* ``kv_on_host=True`` (not a reference argument): the reference's arrangement — cluster-contiguous KV
+  in pinned host memory (:264-274), an LRU page cache of ``cache_cluster_num`` clusters on the GPU
+  (:204-211), a host-side wave buffer per layer (:117-121) and an execution buffer assembled per step
+  (:642-648).  Per layer: scan + select on the GPU, the retrieved ids go to the host (blocking copy,
+  as :575), the wave buffer produces hit/miss page lists, ``gather_copy_and_concat`` reads the missed
+  pages straight from pinned memory, the attend stage runs on the execution buffer, and
+  ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
+
+``use_cluster_estimation`` is accepted for compatibility and ignored.
 """
 from __future__ import annotations
 
@@ -29,7 +40,8 @@ class retroinfer_cache(KV_Cache):
                  num_heads: int, head_dim: int, dtype: torch.dtype, layer_mapping: dict, max_new_length: int,
                  static_pattern_start: int, static_pattern_end: int, core: int, n_centroids: int, n_segment: int,
                  nprobe: int, max_compute_cluster_num: int, cache_unit_size: int, cache_cluster_num: int,
-                 num_gpus: int, model_size: int, use_cluster_estimation: bool = False) -> None:
+                 num_gpus: int, model_size: int, use_cluster_estimation: bool = False,
+                 kv_on_host: bool = False) -> None:
         super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
                          layer_mapping, num_gpus, model_size)
         if head_dim != 128:
@@ -58,6 +70,7 @@ class retroinfer_cache(KV_Cache):
         self.buffer_size = max(int(nprobe * 4), 16) * pages_per_cluster      # :111, page budget per group
         self.list_stride = self.input_length - self.static_pattern_total
 
+        self.kv_on_host = bool(kv_on_host)
         g, c, d = self.batch_groups, n_centroids, head_dim
         self.steady_zone_keys, self.steady_zone_values = [], []
         self.centroids, self.value_sum, self.cluster_size = [], [], []
@@ -75,8 +88,14 @@ class retroinfer_cache(KV_Cache):
             self.cluster_count.append(z(g, c, dt=torch.int32))
             self.cluster_offset.append(z(g, c + 1, dt=torch.int32))
             self.centroids_mask.append(z(g, c, dt=torch.bool))
-            self.list_keys.append(z(batch_size, self.kv_head, self.list_stride, d))
-            self.list_values.append(z(batch_size, self.kv_head, self.list_stride, d))
+            if not self.kv_on_host:
+                self.list_keys.append(z(batch_size, self.kv_head, self.list_stride, d))
+                self.list_values.append(z(batch_size, self.kv_head, self.list_stride, d))
+            else:
+                host = lambda: torch.zeros((batch_size, self.kv_head, self.list_stride, d), dtype=dtype,  # noqa: E731
+                                           pin_memory=True)
+                self.list_keys.append(host())
+                self.list_values.append(host())
 
         self.shape = wave.WaveShape(g, self.group_size, c, nprobe, self.es_cluster_num, self.page_size,
                                     self.buffer_size, self.list_stride, self.static_stride, dtype)
@@ -89,6 +108,40 @@ class retroinfer_cache(KV_Cache):
                 "append_pos": torch.tensor([self.static_pattern_total], dtype=torch.int32, device=dev),
             }
         self._layers = [None] * layer_num
+        if self.kv_on_host:
+            self._init_host_tier(cache_cluster_num)
+
+    def _init_host_tier(self, cache_cluster_num):
+        """GPU page cache, execution buffers, pinned page lists and the host wave buffers
+        (cache_hub/retroinfer_cache.py:117-193, :204-211, :302-316)."""
+        from ..kernels import ThreadPool, WaveBufferCPU
+
+        g, d = self.batch_groups, self.head_dim
+        self.cache_size = max(self.cache_size, 1)
+        self.execution_stride = self.buffer_size * self.page_size + self.static_stride
+        self.thread_pool = ThreadPool(self.core)
+        self.cache_keys, self.cache_values, self.wave_buffer = [], [], []
+        self.page_lists, self.cluster_ids = [], []
+        i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, pin_memory=True)  # noqa: E731
+        for ldx in range(self.layer_num):
+            dev = self.layer_mapping[str(ldx)]
+            self.cache_keys.append(torch.zeros((g, self.cache_size, self.page_size, d), dtype=self.dtype, device=dev))
+            self.cache_values.append(torch.zeros((g, self.cache_size, self.page_size, d), dtype=self.dtype, device=dev))
+            wb = WaveBufferCPU(self.batch_size, self.kv_head, d, self.nprobe, self.page_size, self.n_centroids,
+                               self.n_centroids, self.buffer_size, self.cache_size, self.core, self.thread_pool.get())
+            b = self.buffer_size
+            lists = [i32(g, b), i32(g, b), i32(g, b), i32(g), i32(g, b), i32(g, b), i32(g, b), i32(g),
+                     i32(g, b), i32(g, b), i32(g, b), i32(g)]
+            ids = torch.zeros((g, self.nprobe), dtype=torch.int64, pin_memory=True)
+            wb.set_indices(*lists, ids)
+            self.wave_buffer.append(wb)
+            self.page_lists.append(lists)
+            self.cluster_ids.append(ids)
+        for dev, per in self._per_device.items():
+            per["exec_keys"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
+            per["exec_values"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
+            per["valid_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+        self._keep_alive = []
 
     # ------------------------------------------------------------------ prefill
     def prefill_update_kv_cache(self, query_states, key_states, value_states, layer_idx, batch_idx):
@@ -117,9 +170,12 @@ class retroinfer_cache(KV_Cache):
         self.cluster_count[layer_idx][rows].copy_(r["cluster_count"])
         self.cluster_offset[layer_idx][rows].copy_(r["cluster_offset"])
         self.centroids_mask[layer_idx][rows].copy_(r["cluster_count"] == 0)
-        self.list_keys[layer_idx][batch_idx, :, :valid_length].copy_(r["keys"])
-        self.list_values[layer_idx][batch_idx, :, :valid_length].copy_(r["values"])
+        self.list_keys[layer_idx][batch_idx, :, :valid_length].copy_(r["keys"], non_blocking=self.kv_on_host)
+        self.list_values[layer_idx][batch_idx, :, :valid_length].copy_(r["values"], non_blocking=self.kv_on_host)
         self._error_flags.append(r["error"])
+        if self.kv_on_host:
+            self._keep_alive.append(r)            # sources of the asynchronous device-to-host copies
+            self.wave_buffer[layer_idx].async_construction(None, r["cluster_count"], batch_idx)
 
         if layer_idx == self.layer_num - 1 and batch_idx + bsz == self.batch_size:
             self.context += seq_len
@@ -137,15 +193,25 @@ class retroinfer_cache(KV_Cache):
             if int(flag.item()) != 0:
                 raise RuntimeError(f"clustering gave up on a device-side wait (code {int(flag.item())})")
         self._error_flags.clear()
+        if self.kv_on_host:
+            self._keep_alive.clear()
         g = self.batch_groups
         for ldx in range(self.layer_num):
             per = self._per_device[self.layer_mapping[str(ldx)]]
+            if self.kv_on_host:
+                shape = wave.WaveShape(g, self.group_size, self.n_centroids, self.nprobe, self.es_cluster_num,
+                                       self.page_size, self.buffer_size, self.execution_stride, self.static_stride,
+                                       self.dtype)
+                store_k, store_v = per["exec_keys"], per["exec_values"]
+            else:
+                shape = self.shape
+                store_k = self.list_keys[ldx].view(g, self.list_stride, self.head_dim)
+                store_v = self.list_values[ldx].view(g, self.list_stride, self.head_dim)
             self._layers[ldx] = wave.WaveIndexLayer(
-                self.shape, centroids=self.centroids[ldx], value_sum=self.value_sum[ldx],
+                shape, centroids=self.centroids[ldx], value_sum=self.value_sum[ldx],
                 cluster_size=self.cluster_size[ldx], cluster_count=self.cluster_count[ldx],
-                cluster_offset=self.cluster_offset[ldx],
-                keys=self.list_keys[ldx].view(g, self.list_stride, self.head_dim),
-                values=self.list_values[ldx].view(g, self.list_stride, self.head_dim),
+                cluster_offset=self.cluster_offset[ldx], keys=store_k, values=store_v,
+                want_ids=self.kv_on_host, host_tier=self.kv_on_host,
                 steady_keys=self.steady_zone_keys[ldx].view(g, self.static_stride, self.head_dim),
                 steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
                 static_len=per["static_len"], scratch=per["scratch"])
@@ -172,9 +238,45 @@ class retroinfer_cache(KV_Cache):
     def compute(self, queries, layer_idx, queries_next=None, out=None):
         """Wave-index attention for one layer (:549-697).  queries: [batch, 1, heads, d].
         ``out`` (optional, not in the reference) receives the result instead of a new tensor."""
-        out = self._layers[layer_idx].compute(queries.contiguous(), out)
+        if self.kv_on_host:
+            out = self._compute_host_tier(queries.contiguous(), layer_idx, out)
+        else:
+            out = self._layers[layer_idx].compute(queries.contiguous(), out)
         if layer_idx == self.layer_num - 1:
             # every layer of a step attends static_pattern_total(+1) rows (:559); advance for the next step
             for p in self._per_device.values():
                 p["static_len"].add_(1)
         return out.view(self.batch_size, 1, self.num_heads, self.head_dim)
+
+    def _compute_host_tier(self, queries, layer_idx, out):
+        """One layer with the cluster store in pinned host memory (the reference's steps 1-10,
+        cache_hub/retroinfer_cache.py:558-697)."""
+        from ..kernels import gather_copy_and_concat, gather_copy_and_scatter
+
+        layer, wb = self._layers[layer_idx], self.wave_buffer[layer_idx]
+        per = self._per_device[self.layer_mapping[str(layer_idx)]]
+        g, d = self.batch_groups, self.head_dim
+        if out is None:
+            out = torch.empty_like(queries)
+        static_len = self.static_pattern_total if layer_idx == self.layer_num - 1 else self.static_pattern_total + 1
+        layer.stage("scan", queries, out)
+        layer.stage("select", queries, out)
+        self.cluster_ids[layer_idx].copy_(layer.retrieved_ids)          # blocking device-to-host copy (:575)
+        wb.batch_access()                                                # hit/miss page lists; LRU update in background
+        (hit_ids, hit_sizes, hit_cum, hit_n, miss_ids, miss_sizes, miss_cum, miss_n,
+         upd_buf, upd_sizes, upd_cache, upd_n) = self.page_lists[layer_idx]
+        sk = self.steady_zone_keys[layer_idx].view(g, self.static_stride, d)
+        sv = self.steady_zone_values[layer_idx].view(g, self.static_stride, d)
+        lk = self.list_keys[layer_idx].view(g, self.list_stride, d)
+        lv = self.list_values[layer_idx].view(g, self.list_stride, d)
+        ek, ev, lens = per["exec_keys"], per["exec_values"], per["valid_lengths"]
+        gather_copy_and_concat(sk, lk, self.cache_keys[layer_idx], ek, sv, lv, self.cache_values[layer_idx], ev,
+                               miss_ids, miss_sizes, miss_cum, miss_n, hit_ids, hit_sizes, hit_cum, hit_n, lens, g,
+                               self.static_stride, self.list_stride, self.cache_size, self.execution_stride,
+                               self.buffer_size, static_len)
+        layer.attend_buffer(queries, out, ek, ev, lens)
+        wb.sync()                                                        # update lists are final (:682)
+        gather_copy_and_scatter(ek, self.cache_keys[layer_idx], ev, self.cache_values[layer_idx], upd_buf, upd_sizes,
+                                upd_cache, upd_n, g, self.execution_stride, self.cache_size, self.buffer_size,
+                                static_len)
+        return out

@@ -53,7 +53,7 @@ struct AttendArgs {
   const uint4* steady_v;
   const uint4* value_sum;
   const int32_t* static_len;
-  const int32_t* rows;
+  const int32_t* rows;       // null: exact row i is row i of keys/values (execution-buffer mode)
   const int32_t* n_exact;
   const int32_t* est_ids;
   const float* est_w;
@@ -99,7 +99,7 @@ __global__ void __cluster_dims__(kAttendCluster, 1, 1) __launch_bounds__(128, kC
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
   const int gs = a.gs, es = a.e_steps;
-  const int static_len = *a.static_len;
+  const int static_len = a.static_len ? *a.static_len : 0;   // null: the exact rows already contain the steady zone
   cg::cluster_group cluster = cg::this_cluster();
   constexpr int cpg = kAttendCluster;                    // CTAs per group
   const int groups_per_pass = (int)gridDim.x / cpg;      // clusters in the grid
@@ -133,12 +133,12 @@ __global__ void __cluster_dims__(kAttendCluster, 1, 1) __launch_bounds__(128, kC
       for (int i = 0; i < 4; ++i) {
         const int row = min(base + tt[i], last);
         if (est) id.v[i] = a.est_ids[(int64_t)g * a.e_pad + row];
-        else id.v[i] = row < static_len ? -1 - row : a.rows[(int64_t)g * a.max_rows + row - static_len];
+        else id.v[i] = row < static_len ? -1 - row : (a.rows ? a.rows[(int64_t)g * a.max_rows + row - static_len] : row - static_len);
       }
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
         const int row = min(base + jj * 8 + r, last);
-        id.k[jj] = est ? 0 : (row < static_len ? -1 - row : a.rows[(int64_t)g * a.max_rows + row - static_len]);
+        id.k[jj] = est ? 0 : (row < static_len ? -1 - row : (a.rows ? a.rows[(int64_t)g * a.max_rows + row - static_len] : row - static_len));
       }
       return id;
     };
@@ -358,7 +358,7 @@ int attend_ctas() {
 }
 
 template <int DT>
-int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
+int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb) {
   uint8_t* sc = static_cast<uint8_t*>(p.d_scratch);
   AttendArgs a;
   a.q = static_cast<const uint4*>(p.d_q);
@@ -379,6 +379,14 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
   a.e_steps = (p.n_estimate + 15) / 16;
   a.steady_stride = p.steady_stride; a.max_rows = p.max_exact_rows;
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  if (eb) {   // exact rows = the first lengths[g] rows of a dense buffer that already starts with the steady zone
+    a.keys = static_cast<const uint4*>(eb->keys);
+    a.values = static_cast<const uint4*>(eb->values);
+    a.N = eb->stride;
+    a.n_exact = eb->lengths;
+    a.static_len = nullptr;
+    a.rows = nullptr;
+  }
   const int clusters = min(p.groups, max(1, attend_ctas() / kAttendCluster));
   const int ctas = clusters * kAttendCluster;
   RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
@@ -388,8 +396,8 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
 
 }  // namespace
 
-int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s) {
-  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s) : launch<RI_F16>(p, L, s);
+int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb) {
+  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s, eb) : launch<RI_F16>(p, L, s, eb);
 }
 
 }  // namespace ri_wave

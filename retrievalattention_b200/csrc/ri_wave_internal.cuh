@@ -42,6 +42,8 @@ inline Layout make_layout(const ri_wave_layer& p) {
 // Each launcher enqueues one stage on `s` and returns an ri_status.
 int launch_scan(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
-int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
+// `eb` (optional): attend over a dense execution buffer instead of the cluster-contiguous store.
+struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
+int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr);
 
 }  // namespace ri_wave

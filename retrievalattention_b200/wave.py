@@ -63,7 +63,8 @@ class WaveIndexLayer:
     """One layer's index + KV store with a prepared parameter block for the C ABI."""
 
     def __init__(self, shape: WaveShape, *, centroids, value_sum, cluster_size, cluster_count, cluster_offset,
-                 keys, values, steady_keys, steady_values, static_len, scratch, want_ids: bool = False):
+                 keys, values, steady_keys, steady_values, static_len, scratch, want_ids: bool = False,
+                 host_tier: bool = False):
         self.shape = shape
         dev = centroids.device
         g, c = shape.groups, shape.n_centroids
@@ -71,6 +72,8 @@ class WaveIndexLayer:
         assert cluster_size.shape == (g, c) and cluster_size.dtype == shape.dtype
         assert cluster_count.shape == (g, c) and cluster_count.dtype == torch.int32
         assert cluster_offset.shape == (g, c + 1) and cluster_offset.dtype == torch.int32
+        # host tier: `keys`/`values` are the execution buffers; the cluster store itself is in host memory
+        self.host_tier = host_tier
         assert keys.shape == (g, shape.tokens_per_group, 128) and values.shape == keys.shape
         assert steady_keys.shape == (g, shape.steady_stride, 128) and steady_values.shape == steady_keys.shape
         assert static_len.dtype == torch.int32 and static_len.numel() == 1
@@ -125,6 +128,18 @@ class WaveIndexLayer:
         self._bind(q, out)
         _lib.check(_lib.lib.ri_wave_decode_layer_static(C.byref(self.params), _lib.current_stream()),
                    "ri_wave_decode_layer_static")
+        return out
+
+    def attend_buffer(self, q: torch.Tensor, out: torch.Tensor, exec_keys: torch.Tensor, exec_values: torch.Tensor,
+                      valid_lengths: torch.Tensor) -> torch.Tensor:
+        """Host tier: attend over execution buffers ``[G, stride, 128]`` (steady zone ++ retrieved pages),
+        using the estimation set the select stage left in the scratch."""
+        self._bind(q, out)
+        assert exec_keys.is_cuda and exec_keys.is_contiguous() and exec_values.shape == exec_keys.shape
+        assert valid_lengths.dtype == torch.int32 and valid_lengths.is_cuda
+        _lib.check(_lib.lib.ri_wave_attend_buffer(C.byref(self.params), exec_keys.data_ptr(), exec_values.data_ptr(),
+                                                  exec_keys.shape[1], valid_lengths.data_ptr(), _lib.current_stream()),
+                   "ri_wave_attend_buffer")
         return out
 
     def stage(self, name: str, q: torch.Tensor, out: torch.Tensor) -> None:
