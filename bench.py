@@ -430,9 +430,13 @@ def run_kmeans(geo, args, log):
     keys, values = torch.cat(ks, 0).contiguous(), torch.cat(vs, 0).contiguous()
     del ks, vs
     results = {}
-    for label, segs in (("reference schedule", cfg.n_segment), ("plain Lloyd", 1)):
+    schedules = (("reference schedule", cfg.n_segment),) if args.quick else \
+        (("reference schedule", cfg.n_segment), ("plain Lloyd", 1))
+    for label, segs in schedules:
         warm = max(args.warmup, 3) if segs > 1 else 1
         reps = min(args.steps, 5) if segs > 1 else 2
+        if args.quick:
+            warm, reps = 1, 1
         for _ in range(warm):
             r = build_index(keys, values, cfg.n_centroids, segs, args.kmeans_iters)
         torch.cuda.synchronize()
@@ -473,6 +477,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override layer count (profiling on a small case only)")
     ap.add_argument("--kmeans-iters", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
