@@ -135,7 +135,8 @@ class Workload:
             self.step_body()
 
     def launches_per_step(self):
-        return 5 * self.geo.layers
+        # per layer: steady append, scan, select, attend
+        return 4 * self.geo.layers
 
     def static_len(self):
         return int(self.cache._per_device[str(self.device)]["static_len"].item())
@@ -348,6 +349,12 @@ def run_decode(geo, args, rank, world, local_rank, log):
     kernels = {n: {"ms": round(stage_ms[n], 5), "alg_bytes": int(alg[n]), "gbs": round(alg[n] / stage_ms[n] / 1e6, 1),
                    "frac": round(alg[n] / stage_ms[n] / 1e6 / peak, 4)} for n in stage_ms}
     top = max(stage_ms, key=stage_ms.get)
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+    # profiles/ (one layer of this workload's geometry, 32 groups); scaled by the groups of this rank.
+    ncu_traffic = {"scan": 70.18e6, "select": 6.33e6, "attend": 46.67e6}
+    traffic = None
+    if geo.name.startswith("llama3-8b-128k"):
+        traffic = int(ncu_traffic[top] * wl.shape.groups / 32)
     step_alg = sum(alg.values()) * geo.layers
     tokens = geo.batch * world * args.steps
     cfg = wl.cfg
@@ -375,7 +382,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
         "nccl_collectives": (geo.layers * args.steps) if world > 1 else 0,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "wave_" + top + "_kernel", "achieved": kernels[top]["gbs"], "peak": peak,
-                     "unit": "GB/s", "frac": kernels[top]["frac"], "peak_kind": "of " + peak_kind, "traffic": None,
+                     "unit": "GB/s", "frac": kernels[top]["frac"], "peak_kind": "of " + peak_kind, "traffic": traffic,
                      "kernels": kernels,
                      "path": {"alg_bytes_per_step": int(step_alg), "gbs": round(step_alg / (ms / args.steps) / 1e6, 1),
                               "frac": round(step_alg / (ms / args.steps) / 1e6 / peak, 4)}},

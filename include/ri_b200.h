@@ -84,8 +84,8 @@ typedef struct ri_wave_layer {
 /* Bytes of scratch one ri_wave_decode_layer call needs for this geometry (no device work). */
 int64_t ri_wave_scratch_bytes(const ri_wave_layer* p);
 
-/* Launch scan + select + attend for one layer on `stream`.  The scratch must have been
- * zero-filled once before its first use (the kernels leave it reusable). */
+/* Launch scan + select + attend for one layer on `stream`.  The scratch needs no initialisation:
+ * every stage writes what a later stage reads. */
 int ri_wave_decode_layer(const ri_wave_layer* p, void* stream);
 
 /* Same work as ri_wave_decode_layer for callers that cannot allocate device memory at all: an
@@ -94,8 +94,8 @@ int ri_wave_decode_layer(const ri_wave_layer* p, void* stream);
  * the scratch is a fixed RI_WAVE_STATIC_SCRATCH_BYTES array inside the library image, set aside
  * on every GPU that loads the library until the process exits.  Geometries that need more are
  * refused with RI_ERR_INVALID (config 1 of the benchmark, 32 groups x 8192 centroids, needs
- * about 12 MB).  The call allocates nothing; it clears the part of the array that must start at
- * zero on `stream` and otherwise finds the previous call's leftovers.  All calls share the one
+ * about 8 MB).  The call allocates nothing and finds the previous call's leftovers in the array,
+ * which no stage depends on.  All calls share the one
  * array, so calls whose GPU work overlaps (other streams, unordered threads) race: order them.
  * The first call on each device looks up the array's device address; make it at start-up,
  * before any stream capture.  This entry point has no counterpart in the reference. */

@@ -3,7 +3,7 @@
 // Who needs this: serving runtimes that hand the whole of HBM to their own memory pool when they
 // start (after which a cudaMalloc from a plug-in simply fails), and decode loops that ban driver
 // allocation calls because cudaMalloc and cudaFree stall every stream of the device while they
-// run.  Such a caller has nowhere to get the ~12 MB of scratch that ri_wave_decode_layer expects
+// run.  Such a caller has nowhere to get the ~8 MB of scratch that ri_wave_decode_layer expects
 // in `d_scratch`.  Here the scratch is a fixed array that is part of the library image itself:
 // the driver sets it aside once, when the library is loaded onto a GPU, and it stays there until
 // the process exits.
@@ -11,8 +11,8 @@
 // Rules that follow from sharing one array:
 //  * Geometries whose scratch would exceed RI_WAVE_STATIC_SCRATCH_BYTES are refused.
 //  * Every call (any layer, any stream, any thread) uses the same bytes and finds whatever the
-//    previous call left.  The only part that has to start at zero, the per-group arrival
-//    counters at the front, is cleared on the caller's stream at the start of each call.
+//    previous call left.  That is harmless: each stage writes everything a later stage reads, so
+//    no part of the array has to be initialised.
 //  * Two calls whose GPU work overlaps in time (different streams, or different host threads
 //    without ordering) would overwrite each other's intermediate results.  Order them.
 //  * The device address of the array is looked up on the first call made on each device, with
@@ -59,8 +59,6 @@ extern "C" int ri_wave_decode_layer_static(const ri_wave_layer* p, void* stream)
   void* scratch = nullptr;
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc != RI_OK) return rc;
-  // the arrival counters (one uint32 per group, at the front of the scratch) must start at zero
-  RI_CUDA_OK(cudaMemsetAsync(scratch, 0, (size_t)p->groups * sizeof(uint32_t), static_cast<cudaStream_t>(stream)));
   ri_wave_layer q = *p;
   q.d_scratch = scratch;
   return ri_wave_decode_layer(&q, stream);

@@ -25,7 +25,7 @@ inline Layout make_layout(const ri_wave_layer& p) {
   L.n_tiles = (p.n_centroids + kScanTile - 1) / kScanTile;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { int64_t o = off; off = ri_align_up(off + bytes, 256); return o; };
-  L.counters = take(G * 4);   // reserved word per group at the front (callers zero it once; unused by the kernels)
+  L.counters = take(G * 4);   // reserved word per group at the front (unused by the kernels)
   L.scores = take(G * p.group_size * (int64_t)p.n_centroids * 4);
   L.tile_max = take(G * kMaxHeads * (int64_t)L.n_tiles * 4);
   L.tile_sum = take(G * kMaxHeads * (int64_t)L.n_tiles * 4);

@@ -116,8 +116,8 @@ def test_empty_clusters_rank_last():
 
 
 def test_repeatable_and_scratch_reusable():
-    """Two calls in a row on the same scratch give bit-identical results (the combine
-    counters are left at zero, the selection is deterministic)."""
+    """Two calls in a row on the same scratch give bit-identical results (no stage depends on
+    what the scratch held before, and the selection and the merge order are deterministic)."""
     case = CASES["small_gs4"]
     cpu = build_cpu_index(case)
     layer = to_gpu_layer(case, cpu, SINK + RECENT)
