@@ -9,6 +9,7 @@ needed to build.
 from __future__ import annotations
 
 import os
+import shlex
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
@@ -22,6 +23,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libri_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", f"-I{INCLUDE}", f"-I{CSRC}"]
+NVCC_FLAGS += shlex.split(os.environ.get("RI_NVCC_EXTRA", ""))   # e.g. -DRI_FUSED_TRACE for a timing build
 
 
 def _sources():

@@ -1,5 +1,6 @@
-// C entry points of the fused wave-index decode path: scan -> select -> attend for one layer
-// (kernels in ri_wave_scan.cu, ri_wave_select.cu, ri_wave_attend.cu), plus the steady-zone append.
+// C entry points of the wave-index decode path for one layer: scan -> select -> attend, either as
+// one kernel (ri_wave_fused.cu, the default of ri_wave_decode_layer) or as three stage kernels
+// (ri_wave_scan.cu, ri_wave_select.cu, ri_wave_attend.cu), plus the steady-zone append.
 #include "ri_wave_internal.cuh"
 
 using namespace ri_wave;
@@ -32,9 +33,9 @@ int validate(const ri_wave_layer* p) {
              "KV pointer is null");
   RI_REQUIRE(p->d_q && p->d_out && p->d_scratch, "q/out/scratch pointer is null");
   RI_REQUIRE(((uintptr_t)p->d_centroids | (uintptr_t)p->d_value_sum | (uintptr_t)p->d_keys | (uintptr_t)p->d_values |
-              (uintptr_t)p->d_steady_keys | (uintptr_t)p->d_steady_values | (uintptr_t)p->d_q |
-              (uintptr_t)p->d_scratch) % 16 == 0,
+              (uintptr_t)p->d_steady_keys | (uintptr_t)p->d_steady_values | (uintptr_t)p->d_q) % 16 == 0,
              "tensor pointers must be 16-byte aligned");
+  RI_REQUIRE((uintptr_t)p->d_scratch % 128 == 0, "the scratch must be 128-byte aligned");
   return RI_OK;
 }
 
@@ -107,6 +108,9 @@ extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
   if (rc != RI_OK) return rc;
   const Layout L = make_layout(*p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // RI_WAVE_STAGED=1 keeps the three-kernel form (profiling one stage at a time, A/B timing)
+  static const bool staged = getenv("RI_WAVE_STAGED") && atoi(getenv("RI_WAVE_STAGED")) != 0;
+  if (!staged && fused_supported(*p)) return launch_fused(*p, L, s);
   if ((rc = launch_scan(*p, L, s)) != RI_OK) return rc;
   if ((rc = launch_select(*p, L, s)) != RI_OK) return rc;
   return launch_attend(*p, L, s);

@@ -13,6 +13,22 @@ constexpr int kMaxHeads = 8;        // GQA group size limit (N dimension of the 
 constexpr int kAttendMaxCtas = 512; // persistent attend CTAs (2 per SM) the scratch is sized for; 4 warps each
 constexpr int kAttendMaxGroups = 4096;
 
+// Timing build (-DRI_FUSED_TRACE): thread 0 of every CTA of the single-kernel path stamps the global
+// timer at phase boundaries; ri_debug_fused_trace() copies the stamps out.  Compiled out otherwise.
+#ifdef RI_FUSED_TRACE
+static __device__ unsigned long long g_ftrace[4096 * 32];
+__device__ __forceinline__ void ri_ft(int k) {
+  if (threadIdx.x == 0 && gridDim.y * gridDim.x <= 4096) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + k] = t;
+  }
+}
+#define RI_FT(k) ri_ft(k)
+#else
+#define RI_FT(k)
+#endif
+
 struct Layout {
   int64_t counters, scores, tile_max, tile_sum, dist_keys, est_ids, est_w, est_s2, rows, n_exact, total;
   int e_pad, n_tiles;
@@ -21,7 +37,10 @@ struct Layout {
 inline Layout make_layout(const ri_wave_layer& p) {
   Layout L;
   const int64_t G = p.groups;
-  L.e_pad = (int)ri_align_up(p.n_estimate > 0 ? p.n_estimate : 1, 16);
+  // Per-group strides of the estimation lists are whole 128-byte lines: in the single-kernel path a
+  // list is written and read inside one launch, and an SM's L1 must never hold a line that another
+  // group's cluster is still going to write.
+  L.e_pad = (int)ri_align_up(p.n_estimate > 0 ? p.n_estimate : 1, 32);
   L.n_tiles = (p.n_centroids + kScanTile - 1) / kScanTile;
   int64_t off = 0;
   auto take = [&](int64_t bytes) { int64_t o = off; off = ri_align_up(off + bytes, 256); return o; };
@@ -45,5 +64,8 @@ int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 // `eb` (optional): attend over a dense execution buffer instead of the cluster-contiguous store.
 struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
 int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr);
+// scan + select + attend as one kernel (one 8-CTA cluster per group).
+int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
+bool fused_supported(const ri_wave_layer& p);   // geometries the single kernel covers (others run the three stages)
 
 }  // namespace ri_wave

@@ -110,11 +110,20 @@ class WaveIndexLayer:
         self.params.d_q, self.params.d_out = q.data_ptr(), out.data_ptr()
 
     def compute(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """scan + select + attend on the current stream.  ``q``: [B, 1, Hq, 128] (or [G, gs, 128])."""
+        """scan + select + attend (one kernel) on the current stream.  ``q``: [B, 1, Hq, 128] (or [G, gs, 128])."""
         if out is None:
             out = torch.empty_like(q)
         self._bind(q, out)
         _lib.check(_lib.lib.ri_wave_decode_layer(C.byref(self.params), _lib.current_stream()), "ri_wave_decode_layer")
+        return out
+
+    def compute_staged(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The same step as three stage kernels (scan, select, attend) instead of the single kernel
+        ``compute`` launches — profiling one stage at a time, and a cross-check of the two forms."""
+        if out is None:
+            out = torch.empty_like(q)
+        for name in ("scan", "select", "attend"):
+            self.stage(name, q, out)
         return out
 
     def compute_static(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -4,6 +4,8 @@ CPU oracle on the same seeded inputs.
 Bars: centroid scores within fp32 accumulation noise; distance keys and selected sets bit-exact
 except where distances tie within 1e-3 of the cut; attention output max-abs <= 2e-2 and
 mean-abs <= 2e-3 against the oracle's fp32 evaluation."""
+import os
+
 import pytest
 import torch
 
@@ -37,8 +39,9 @@ def ordered_key(dist: torch.Tensor) -> torch.Tensor:
     return torch.where(bits >= 0x8000, (~bits) & 0xFFFF, bits | 0x8000)
 
 
+@pytest.mark.parametrize("mode", ["single_kernel", "single_kernel_global_lists", "staged"])
 @pytest.mark.parametrize("name", sorted(CASES))
-def test_fused_decode_matches_oracle(name):
+def test_fused_decode_matches_oracle(name, mode):
     case = CASES[name]
     cpu = build_cpu_index(case)
     static_len = SINK + RECENT + 1
@@ -49,7 +52,16 @@ def test_fused_decode_matches_oracle(name):
     q = queries(case)
     ref_out, parts = run_oracle(case, cpu, q, static_len)
 
-    out = layer.compute(q.cuda())
+    if mode == "staged":
+        out = layer.compute_staged(q.cuda())
+    elif mode == "single_kernel":
+        out = layer.compute(q.cuda())
+    else:   # no room for estimation entries in shared memory: the kernel falls back to its global lists
+        os.environ["RI_WAVE_LOCAL_CAP"] = "0"
+        try:
+            out = layer.compute(q.cuda())
+        finally:
+            del os.environ["RI_WAVE_LOCAL_CAP"]
     torch.cuda.synchronize()
     v = layer.views()
 
