@@ -39,6 +39,7 @@ from retrievalattention_b200.synthetic import make_kv  # noqa: E402
 SINK, RECENT = 4, 64
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+NCU_TRAFFIC_DECODE = 118.4e6   # dram__bytes_read.sum + dram__bytes_write.sum per launch of wave_fused_kernel (profiles/wave_fused_cfg1_2layers.md)
 METRIC = "decode tok/s at 128K ctx (Llama-3-8B geometry); attn kernel HBM GB/s vs peak"
 
 
@@ -135,8 +136,9 @@ class Workload:
             self.step_body()
 
     def launches_per_step(self):
-        # per layer: steady append, scan, select, attend
-        return 4 * self.geo.layers
+        # per layer: steady append, then the single decode kernel (RI_WAVE_STAGED=1: scan, select, attend)
+        staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")
+        return (4 if staged else 2) * self.geo.layers
 
     def static_len(self):
         return int(self.cache._per_device[str(self.device)]["static_len"].item())
@@ -200,25 +202,27 @@ def algorithmic_bytes(wl, n_ret_rows, static_len):
 
 
 def time_stages(wl, first_step, steps):
-    """Device time of each stage, averaged over layers and steps.  Three CUDA graphs replay the
-    stage prefixes scan / scan+select / scan+select+attend over ALL layers (so every launch works
-    on cold data, as in the real step, and no host launch gap is timed); a stage's time is the
-    difference between consecutive prefixes, so the three numbers add up to the attention part of
-    the step."""
+    """Device time per layer of the single decode kernel, and of each stage of the three-kernel
+    form, averaged over layers and steps.  CUDA graphs replay, over ALL layers (so every launch
+    works on cold data, as in the real step, and no host launch gap is timed), the single kernel
+    and the stage prefixes scan / scan+select / scan+select+attend; a stage's time is the
+    difference between consecutive prefixes."""
     names = ("scan", "select", "attend")
     layers = wl.cache._layers
     graphs = []
     wl.q_in.copy_(wl.q_all[first_step]); wl.k_in.copy_(wl.k_all[first_step]); wl.v_in.copy_(wl.v_all[first_step])
-    for upto in range(1, 4):
-        for l, layer in enumerate(layers):           # warm (and validate) outside capture
-            for n in names[:upto]:
-                layer.stage(n, wl.q_in[l], wl.out[l])
+    for upto in range(0, 4):
+        def body():
+            for l, layer in enumerate(layers):
+                if upto == 0:
+                    layer.compute(wl.q_in[l], wl.out[l])      # what the step launches (ri_wave_decode_layer)
+                for n in names[:upto]:
+                    layer.stage(n, wl.q_in[l], wl.out[l])
+        body()                                       # warm (and validate) outside capture
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            for l, layer in enumerate(layers):
-                for n in names[:upto]:
-                    layer.stage(n, wl.q_in[l], wl.out[l])
+            body()
         graphs.append(g)
     prefix_ms = []
     for g in graphs:
@@ -232,7 +236,8 @@ def time_stages(wl, first_step, steps):
         b.record()
         torch.cuda.synchronize()
         prefix_ms.append(a.elapsed_time(b) / (steps * len(layers)))
-    ms = {"scan": prefix_ms[0], "select": prefix_ms[1] - prefix_ms[0], "attend": prefix_ms[2] - prefix_ms[1]}
+    ms = {"decode": prefix_ms[0], "scan": prefix_ms[1], "select": prefix_ms[2] - prefix_ms[1],
+          "attend": prefix_ms[3] - prefix_ms[2]}
     n_ret = 0
     for l, layer in enumerate(layers):
         for n in names[:2]:
@@ -346,16 +351,19 @@ def run_decode(geo, args, rank, world, local_rank, log):
         return
     peak, _, peak_kind = measured_peaks()
     alg = algorithmic_bytes(wl, n_ret_rows, static_len)
+    staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")   # the library's switch to the three-kernel form
+    alg["decode"] = sum(alg.values())                # the single kernel does all three stages' work
     kernels = {n: {"ms": round(stage_ms[n], 5), "alg_bytes": int(alg[n]), "gbs": round(alg[n] / stage_ms[n] / 1e6, 1),
                    "frac": round(alg[n] / stage_ms[n] / 1e6 / peak, 4)} for n in stage_ms}
-    top = max(stage_ms, key=stage_ms.get)
+    top = max(("scan", "select", "attend"), key=stage_ms.get) if staged else "decode"
+    kernel_name = {"decode": "wave_fused_kernel"}.get(top, "wave_" + top + "_kernel")
     # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
     # profiles/ (one layer of this workload's geometry, 32 groups); scaled by the groups of this rank.
-    ncu_traffic = {"scan": 70.18e6, "select": 6.33e6, "attend": 46.67e6}
+    ncu_traffic = {"decode": NCU_TRAFFIC_DECODE, "scan": 70.18e6, "select": 6.33e6, "attend": 46.67e6}
     traffic = None
-    if geo.name.startswith("llama3-8b-128k"):
+    if geo.name.startswith("llama3-8b-128k") and ncu_traffic[top]:
         traffic = int(ncu_traffic[top] * wl.shape.groups / 32)
-    step_alg = sum(alg.values()) * geo.layers
+    step_alg = alg["decode"] * geo.layers
     tokens = geo.batch * world * args.steps
     cfg = wl.cfg
     lg = wl.geo
@@ -381,9 +389,12 @@ def run_decode(geo, args, rank, world, local_rank, log):
         "gpu_launches": wl.launches_per_step() * args.steps,
         "nccl_collectives": (geo.layers * args.steps) if world > 1 else 0,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "wave_" + top + "_kernel", "achieved": kernels[top]["gbs"], "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": kernels[top]["gbs"], "peak": peak,
                      "unit": "GB/s", "frac": kernels[top]["frac"], "peak_kind": "of " + peak_kind, "traffic": traffic,
                      "kernels": kernels,
+                     "kernels_note": "decode = the one kernel per layer the step launches (wave_fused_kernel); scan/select/"
+                                     "attend = the same work as three stage kernels (RI_WAVE_STAGED=1); all are marginal "
+                                     "times per layer from CUDA graphs over all layers",
                      "path": {"alg_bytes_per_step": int(step_alg), "gbs": round(step_alg / (ms / args.steps) / 1e6, 1),
                               "frac": round(step_alg / (ms / args.steps) / 1e6 / peak, 4)}},
     }

@@ -175,6 +175,7 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   __shared__ uint32_t hist1[128], hist2a[128], hist2b[128];
   __shared__ __align__(16) int s_cnt[4];          // this CTA's keys above the K cut | above the P cut | on the K cut | on the P cut
   __shared__ int s_before[4];       // the same four, summed over the CTAs of lower rank
+  __shared__ int s_share[4];        // this CTA's exact steps [lo, hi), its estimation entries, whether the lists fit
   __shared__ int s_nret[kSelectCluster], s_nest[kSelectCluster];   // every CTA's candidates / estimation entries
   __shared__ int fk[3], fp[3], lk[3], lp[3];
   __shared__ uint32_t warp_sums[T / 32];
@@ -370,11 +371,10 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
     s_nest[tid] = pub.y;
   }
   __syncthreads();
-  int nest[kSelectCluster];
   {
     int nret[kSelectCluster];
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) { nret[rr] = s_nret[rr]; nest[rr] = s_nest[rr]; }
+    for (int rr = 0; rr < kSelectCluster; ++rr) nret[rr] = s_nret[rr];
     for (int i = tid; i < a.p_pad; i += T) {
       int src = 0, j = i, lim = nret[0];     // candidate i of the group = candidate j of CTA src, which holds lim
 #pragma unroll
@@ -386,27 +386,36 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
     }
   }
   __syncthreads();
+  cluster_arrive();     // this CTA's remote reads of the other CTAs' `own` lists are over (awaited before the ring is reused)
   RI_FT(16);
-  for (int i = tid; i < a.P; i += T) {
-    const uint32_t mine = cand[i];
-    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;      // distinct values: distinct ranks
-    int j = 0;
-    for (; j + 16 <= a.p_pad; j += 16) {
-      const uint4 c0 = *reinterpret_cast<const uint4*>(cand + j), c1 = *reinterpret_cast<const uint4*>(cand + j + 4);
-      const uint4 c2 = *reinterpret_cast<const uint4*>(cand + j + 8), c3 = *reinterpret_cast<const uint4*>(cand + j + 12);
-      r0 += (c0.x > mine) + (c0.y > mine) + (c0.z > mine) + (c0.w > mine);
-      r1 += (c1.x > mine) + (c1.y > mine) + (c1.z > mine) + (c1.w > mine);
-      r2 += (c2.x > mine) + (c2.y > mine) + (c2.z > mine) + (c2.w > mine);
-      r3 += (c3.x > mine) + (c3.y > mine) + (c3.z > mine) + (c3.w > mine);
+  {
+    // rank = number of larger candidates (distinct values: distinct ranks); four lanes share a candidate,
+    // each counting over a quarter of the list
+    const int quads = a.p_pad / 4, seg = tid & 3;
+    const int q_lo = quads * seg / 4, q_hi = quads * (seg + 1) / 4;
+    for (int base = 0; base < a.P; base += T / 4) {      // uniform trip count: the shuffles below need whole warps
+      const int i = base + (tid >> 2);
+      const uint32_t mine = i < a.P ? cand[i] : 0xffffffffu;
+      int r0 = 0, r1 = 0;
+      int q = q_lo;
+      for (; q + 2 <= q_hi; q += 2) {
+        const uint4 c0 = *reinterpret_cast<const uint4*>(cand + 4 * q), c1 = *reinterpret_cast<const uint4*>(cand + 4 * q + 4);
+        r0 += (c0.x > mine) + (c0.y > mine) + (c0.z > mine) + (c0.w > mine);
+        r1 += (c1.x > mine) + (c1.y > mine) + (c1.z > mine) + (c1.w > mine);
+      }
+      if (q < q_hi) {
+        const uint4 c = *reinterpret_cast<const uint4*>(cand + 4 * q);
+        r0 += (c.x > mine) + (c.y > mine) + (c.z > mine) + (c.w > mine);
+      }
+      int rk = r0 + r1;
+      rk += __shfl_xor_sync(0xffffffffu, rk, 1);
+      rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+      if (seg == 0 && i < a.P) {
+        ranked[rk] = mine;
+        rcnt[rk] = cand_cnt[i];
+        roff[rk] = cand_off[i];
+      }
     }
-    for (; j < a.p_pad; j += 4) {
-      const uint4 c = *reinterpret_cast<const uint4*>(cand + j);
-      r0 += (c.x > mine) + (c.y > mine) + (c.z > mine) + (c.w > mine);
-    }
-    const int rk = r0 + r1 + r2 + r3;
-    ranked[rk] = mine;
-    rcnt[rk] = cand_cnt[i];
-    roff[rk] = cand_off[i];
   }
   __syncthreads();
   RI_FT(17);
@@ -454,46 +463,47 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
     dstart[i] = i < keep ? rstart[i] : (uint32_t)rows_kept;
     if (i < keep) doff[i] = roff[i];
   }
-  int est_max = 0;
-#pragma unroll
-  for (int rr = 0; rr < kSelectCluster; ++rr) est_max = max(est_max, nest[rr]);
-  const bool local = est_max <= f.cap;
-  {
-    // level the cost units (kCostEst per estimation step a CTA already has, kCostExact per exact step to hand
-    // out): find the level T with sum_c max(0, T - e_c) >= X, then cut the exact steps at the running sums
+  // Share out the exact steps: level the cost units (kCostEst per estimation step a CTA already has,
+  // kCostExact per exact step to hand out) so that sum_c max(0, level - e_c) >= X, then cut the exact steps at the
+  // running sums.  Lane c of warp 0 stands for CTA c.  Two rounds of levelling (CTAs above the first level drop
+  // out of the second) are enough in practice; whatever imbalance is left only costs time.
+  if (warp == 0) {
     const int xs_total = (static_len + rows_kept + 15) / 16;
     const int X = kCostExact * xs_total;
-    int e_u[kSelectCluster];
-#pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) e_u[rr] = kCostEst * ((nest[rr] + 15) / 16);
-    // two rounds of levelling (CTAs above the first level drop out of the second) are enough in practice;
-    // whatever imbalance is left only costs time
+    const int n_e = lane < kSelectCluster ? s_nest[lane] : 0;
+    const int e_u = kCostEst * ((n_e + 15) / 16);
+    bool act = lane < kSelectCluster;
     int level = 0;
-    uint32_t active = (1u << kSelectCluster) - 1;
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
-      int sum_e = 0, n = 0;
+      int sum_e = act ? e_u : 0;
 #pragma unroll
-      for (int rr = 0; rr < kSelectCluster; ++rr)
-        if (active >> rr & 1u) { sum_e += e_u[rr]; ++n; }
-      level = (int)__fdividef((float)(X + sum_e + n - 1), (float)n);     // n >= 1: the CTA with the least work stays
-#pragma unroll
-      for (int rr = 0; rr < kSelectCluster; ++rr)
-        if (e_u[rr] > level) active &= ~(1u << rr);
+      for (int o = 4; o > 0; o >>= 1) sum_e += __shfl_xor_sync(0xffffffffu, sum_e, o);   // lanes 0..7 hold the sum
+      sum_e = __shfl_sync(0xffffffffu, sum_e, 0);
+      const int n = __popc(__ballot_sync(0xffffffffu, act));                             // >= 1: the least loaded CTA stays
+      level = (int)__fdividef((float)(X + sum_e + n - 1), (float)n);
+      act = act && e_u <= level;
     }
-    int cum = 0, my_lo = 0, my_hi = 0, my_est = 0;
+    const int x_u = lane < kSelectCluster ? max(0, level - e_u) : 0;
+    int incl = x_u;
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) {
-      const int b_lo = min(xs_total, (cum + kCostExact - 1) / kCostExact);
-      cum += max(0, level - e_u[rr]);
-      const int b_hi = rr == kSelectCluster - 1 ? xs_total : min(xs_total, (cum + kCostExact - 1) / kCostExact);
-      if (rr == rank) { my_lo = b_lo; my_hi = b_hi; my_est = nest[rr]; }
+    for (int o = 1; o < kSelectCluster; o <<= 1) {
+      const int nb = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += nb;
     }
-    ll.est_idx = est_idx; ll.est_wt = est_wt; ll.est_sc = est_sc;
-    ll.cap = f.cap; ll.n_est = my_est; ll.slice_lo = lo;
-    ll.dstart = dstart; ll.doff = doff; ll.keep = keep; ll.n_rows = rows_kept;
-    ll.x_lo = my_lo; ll.x_hi = my_hi;
+    const int b_lo = min(xs_total, (incl - x_u + kCostExact - 1) / kCostExact);
+    const int b_hi = lane == kSelectCluster - 1 ? xs_total : min(xs_total, (incl + kCostExact - 1) / kCostExact);
+    int est_max = n_e;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) est_max = max(est_max, __shfl_xor_sync(0xffffffffu, est_max, o));
+    if (lane == rank) { s_share[0] = b_lo; s_share[1] = b_hi; s_share[2] = n_e; s_share[3] = est_max <= f.cap; }
   }
+  __syncthreads();
+  const bool local = s_share[3] != 0;
+  ll.est_idx = est_idx; ll.est_wt = est_wt; ll.est_sc = est_sc;
+  ll.cap = f.cap; ll.n_est = s_share[2]; ll.slice_lo = lo;
+  ll.dstart = dstart; ll.doff = doff; ll.keep = keep; ll.n_rows = rows_kept;
+  ll.x_lo = s_share[0]; ll.x_hi = s_share[1];
 
   RI_FT(18);
   // ---- the global lists: for callers that asked for them, and for the attend body when the lists above
@@ -530,9 +540,12 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       if (a.retrieved_ids)
         for (int i = tid; i < a.P; i += T) a.retrieved_ids[(int64_t)g * a.P + i] = 0xffff - (int)(ranked[i] & 0xffffu);
     }
-    if (!local) __threadfence();      // read by the other CTAs of the cluster in the next phase
   }
-  cluster.sync();     // remote reads of `own` are over (the ring is about to be reused); global lists are published
+  cluster_wait();       // every CTA is done reading this CTA's `own` list: the ring may be reused
+  if (!local) {         // the global lists are read by the other CTAs of the cluster in the next phase
+    __threadfence();
+    cluster.sync();
+  }
   return local;
 }
 

@@ -16,12 +16,13 @@ constexpr int kAttendMaxGroups = 4096;
 // Timing build (-DRI_FUSED_TRACE): thread 0 of every CTA of the single-kernel path stamps the global
 // timer at phase boundaries; ri_debug_fused_trace() copies the stamps out.  Compiled out otherwise.
 #ifdef RI_FUSED_TRACE
-static __device__ unsigned long long g_ftrace[4096 * 32];
+static __device__ unsigned long long g_ftrace[4096 * 64];
 __device__ __forceinline__ void ri_ft(int k) {
   if (threadIdx.x == 0 && gridDim.y * gridDim.x <= 4096) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + k] = t;
+    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 64 + k] = t;
+    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 64 + 32 + k] = (unsigned long long)clock64();
   }
 }
 #define RI_FT(k) ri_ft(k)
