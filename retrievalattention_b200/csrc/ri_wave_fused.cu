@@ -540,6 +540,7 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       if (a.retrieved_ids)
         for (int i = tid; i < a.P; i += T) a.retrieved_ids[(int64_t)g * a.P + i] = 0xffff - (int)(ranked[i] & 0xffffu);
     }
+    __syncthreads();    // the arrays read above lie in a ring slot that a faster warp is about to fill
   }
   cluster_wait();       // every CTA is done reading this CTA's `own` list: the ring may be reused
   if (!local) {         // the global lists are read by the other CTAs of the cluster in the next phase
