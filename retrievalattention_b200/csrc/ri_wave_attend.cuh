@@ -46,7 +46,8 @@ constexpr int kAttendCluster = 8;   // CTAs per group
 #define RI_COST_EST 2
 #define RI_COST_EXACT 3
 #endif
-constexpr int kCostEst = RI_COST_EST, kCostExact = RI_COST_EXACT;   // relative cost of a step (bytes moved)
+// relative cost of a step when the steps of a group are shared out (an estimation step moves half the bytes of an
+// exact one); RI_COST_EST / RI_COST_EXACT in the environment override them (tuning)
 constexpr int kStageBytes = 16 * 32 * 16;       // 16 pieces x 32 lanes x 16 bytes = 8 KB per warp and stage
 constexpr int kRingBytes = 4 * kStages * kStageBytes;
 
@@ -67,6 +68,7 @@ struct AttendArgs {
   int64_t N;
   int G, C, gs, E, e_pad, e_steps, steady_stride, max_rows;
   float scale2;        // log2(e) / sqrt(d)
+  int cost_est, cost_exact;   // relative cost of an estimation / exact step when the steps are shared out
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -138,6 +140,7 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
   const int n_est_rows = LOCAL ? ll->n_est : a.E;
   // cost units: kCostEst per estimation step, kCostExact per exact step; a step belongs to the warp holding
   // its first unit (an estimation step moves half the bytes but costs about two thirds of the time, measured)
+  const int kCostEst = a.cost_est, kCostExact = a.cost_exact;
   const int units = kCostEst * es + kCostExact * xs;
   const int n_w = LOCAL ? 4 : cpg * 4, wl = LOCAL ? warp : cl * 4 + warp;
   const int per = max(kCostExact, (units + n_w - 1) / n_w);
@@ -436,6 +439,10 @@ inline void fill_attend_args(const ri_wave_layer& p, const Layout& L, const Exec
   a.e_steps = (p.n_estimate + 15) / 16;
   a.steady_stride = p.steady_stride; a.max_rows = p.max_exact_rows;
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  static const int cost_est = getenv("RI_COST_EST") ? atoi(getenv("RI_COST_EST")) : RI_COST_EST;
+  static const int cost_exact = getenv("RI_COST_EXACT") ? atoi(getenv("RI_COST_EXACT")) : RI_COST_EXACT;
+  a.cost_est = cost_est > 0 ? cost_est : 1;
+  a.cost_exact = cost_exact > 0 ? cost_exact : 1;
   if (eb) {   // exact rows = the first lengths[g] rows of a dense buffer that already starts with the steady zone
     a.keys = static_cast<const uint4*>(eb->keys);
     a.values = static_cast<const uint4*>(eb->values);

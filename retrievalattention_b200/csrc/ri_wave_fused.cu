@@ -388,51 +388,63 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   __syncthreads();
   cluster_arrive();     // this CTA's remote reads of the other CTAs' `own` lists are over (awaited before the ring is reused)
   RI_FT(16);
-  {
-    // rank = number of larger candidates (distinct values: distinct ranks); four lanes share a candidate,
-    // each counting over a quarter of the list
-    const int quads = a.p_pad / 4, seg = tid & 3;
-    const int q_lo = quads * seg / 4, q_hi = quads * (seg + 1) / 4;
-    for (int base = 0; base < a.P; base += T / 4) {      // uniform trip count: the shuffles below need whole warps
-      const int i = base + (tid >> 2);
-      const uint32_t mine = i < a.P ? cand[i] : 0xffffffffu;
-      int r0 = 0, r1 = 0;
-      int q = q_lo;
-      for (; q + 2 <= q_hi; q += 2) {
-        const uint4 c0 = *reinterpret_cast<const uint4*>(cand + 4 * q), c1 = *reinterpret_cast<const uint4*>(cand + 4 * q + 4);
-        r0 += (c0.x > mine) + (c0.y > mine) + (c0.z > mine) + (c0.w > mine);
-        r1 += (c1.x > mine) + (c1.y > mine) + (c1.z > mine) + (c1.w > mine);
-      }
-      if (q < q_hi) {
-        const uint4 c = *reinterpret_cast<const uint4*>(cand + 4 * q);
-        r0 += (c.x > mine) + (c.y > mine) + (c.z > mine) + (c.w > mine);
-      }
-      int rk = r0 + r1;
-      rk += __shfl_xor_sync(0xffffffffu, rk, 1);
-      rk += __shfl_xor_sync(0xffffffffu, rk, 2);
-      if (seg == 0 && i < a.P) {
-        ranked[rk] = mine;
-        rcnt[rk] = cand_cnt[i];
-        roff[rk] = cand_off[i];
-      }
-    }
-  }
-  __syncthreads();
-  RI_FT(17);
-  {
-    constexpr int kPer = 1024 / T;    // P <= 1024
-    int pc[kPer], pages[kPer];
-    uint32_t psum = 0;
+  // Page budget (wave_buffer_cpu.cpp:207-216): the clusters are taken in rank order while their pages fit.
+  // When ALL P candidates fit — the usual case — the order plays no part in what is attended, so unless the
+  // caller wants the ranked ids the ranking is skipped and the rows are laid out in cluster-id order.
+  constexpr int kPer = 1024 / T;    // P <= 1024
+  int pc[kPer], pages[kPer];
+  uint32_t psum, total, before;
+  auto count_pages = [&](const uint32_t* sizes) {
+    psum = 0;
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int i = tid * kPer + u;
-      pc[u] = i < a.P ? (int)rcnt[i] : 0;
+      pc[u] = i < a.P ? (int)sizes[i] : 0;
       pages[u] = (pc[u] + a.page - 1) / a.page;
       psum += (uint32_t)pages[u];
     }
-    uint32_t total;
-    uint32_t before = block_scan<T, uint32_t>(psum, warp_sums, total);
-    // pages are non-negative, so the clusters that fit the budget form a prefix of the ranking
+    before = block_scan<T, uint32_t>(psum, warp_sums, total);
+  };
+  count_pages(cand_cnt);
+  if (f.views || (int)total > a.buffer_pages) {
+    {
+      // rank = number of larger candidates (distinct values: distinct ranks); four lanes share a candidate,
+      // each counting over a quarter of the list
+      const int quads = a.p_pad / 4, seg = tid & 3;
+      const int q_lo = quads * seg / 4, q_hi = quads * (seg + 1) / 4;
+      for (int base = 0; base < a.P; base += T / 4) {      // uniform trip count: the shuffles below need whole warps
+        const int i = base + (tid >> 2);
+        const uint32_t mine = i < a.P ? cand[i] : 0xffffffffu;
+        int r0 = 0, r1 = 0;
+        int q = q_lo;
+        for (; q + 2 <= q_hi; q += 2) {
+          const uint4 c0 = *reinterpret_cast<const uint4*>(cand + 4 * q), c1 = *reinterpret_cast<const uint4*>(cand + 4 * q + 4);
+          r0 += (c0.x > mine) + (c0.y > mine) + (c0.z > mine) + (c0.w > mine);
+          r1 += (c1.x > mine) + (c1.y > mine) + (c1.z > mine) + (c1.w > mine);
+        }
+        if (q < q_hi) {
+          const uint4 c = *reinterpret_cast<const uint4*>(cand + 4 * q);
+          r0 += (c.x > mine) + (c.y > mine) + (c.z > mine) + (c.w > mine);
+        }
+        int rk = r0 + r1;
+        rk += __shfl_xor_sync(0xffffffffu, rk, 1);
+        rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+        if (seg == 0 && i < a.P) {
+          ranked[rk] = mine;
+          rcnt[rk] = cand_cnt[i];
+          roff[rk] = cand_off[i];
+        }
+      }
+    }
+    __syncthreads();
+    count_pages(rcnt);
+  } else {
+    rcnt = cand_cnt;      // id order serves as the order of the row list
+    roff = cand_off;
+  }
+  RI_FT(17);
+  {
+    // pages are non-negative, so the clusters that fit the budget form a prefix of the order
     bool fits[kPer];
     uint32_t nfit = 0, rsum = 0;
 #pragma unroll
@@ -469,9 +481,9 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   // out of the second) are enough in practice; whatever imbalance is left only costs time.
   if (warp == 0) {
     const int xs_total = (static_len + rows_kept + 15) / 16;
-    const int X = kCostExact * xs_total;
+    const int X = f.att.cost_exact * xs_total;
     const int n_e = lane < kSelectCluster ? s_nest[lane] : 0;
-    const int e_u = kCostEst * ((n_e + 15) / 16);
+    const int e_u = f.att.cost_est * ((n_e + 15) / 16);
     bool act = lane < kSelectCluster;
     int level = 0;
 #pragma unroll
@@ -491,8 +503,8 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       const int nb = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += nb;
     }
-    const int b_lo = min(xs_total, (incl - x_u + kCostExact - 1) / kCostExact);
-    const int b_hi = lane == kSelectCluster - 1 ? xs_total : min(xs_total, (incl + kCostExact - 1) / kCostExact);
+    const int b_lo = min(xs_total, (incl - x_u + f.att.cost_exact - 1) / f.att.cost_exact);
+    const int b_hi = lane == kSelectCluster - 1 ? xs_total : min(xs_total, (incl + f.att.cost_exact - 1) / f.att.cost_exact);
     int est_max = n_e;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) est_max = max(est_max, __shfl_xor_sync(0xffffffffu, est_max, o));
