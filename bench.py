@@ -99,19 +99,36 @@ class Workload:
         self.v_in = torch.zeros(shp_kv[1:], dtype=torch.bfloat16, device=device)
         self.out = torch.zeros(shp_q[1:], dtype=torch.bfloat16, device=device)
         self.gathered = None
+        self.peer = None
         if self.gather is not None:
-            self.gathered = torch.zeros((geo.layers, self.shard.head_shards) + tuple(shp_q[2:]), dtype=torch.bfloat16,
-                                        device=device)
+            # the gather of the head slices: done by the decode kernel itself through peer-mapped buffers
+            # (PeerGather); RI_GATHER=nccl, or a failed set-up of those buffers, selects the NCCL all-gather
+            if os.environ.get("RI_GATHER", "peer") != "nccl":
+                try:
+                    from retrievalattention_b200.head_shard import PeerGather
+                    self.peer = PeerGather(self.shard, geo.layers, geo.batch, geo.q_heads, geo.head_dim, torch.bfloat16,
+                                           device, group=self.gather.group)
+                except Exception as exc:     # noqa: BLE001 — any set-up failure falls back to the collective
+                    self.peer_error = repr(exc)[:200]
+                    if log:
+                        log("peer-store gather unavailable, using NCCL: " + self.peer_error)
+            if self.peer is None:
+                self.gathered = torch.zeros((geo.layers, self.shard.head_shards) + tuple(shp_q[2:]),
+                                            dtype=torch.bfloat16, device=device)
         self.graph = None
 
     def step_body(self):
         """One decode step of the hot path over all layers on the current stream: per layer the
-        reference's two calls (model_hub/LLM.py:116-117).  5 kernels of this library per layer:
-        steady append, scan, select, attend, combine."""
+        reference's two calls (model_hub/LLM.py:116-117): the steady append and the decode kernel.
+        Several GPUs: the head slices of all ranks -> [B, 1, Hq, d] for the output projection, either
+        written by the decode kernel into every rank's buffer (then one bounded flag wait per layer) or
+        by an NCCL all-gather."""
         for l in range(self.geo.layers):
             self.cache.decode_update_kv_cache(self.k_in[l], self.v_in[l], l)
-            self.cache.compute(self.q_in[l], l, out=self.out[l])
-            if self.gather is not None:      # head slices of all ranks -> [B, 1, Hq, d] for o_proj
+            self.cache.compute(self.q_in[l], l, out=self.out[l], gather=self.peer)
+            if self.peer is not None:
+                self.peer.wait(l)
+            elif self.gather is not None:
                 self.gather(self.out[l], self.gathered[l])
 
     def capture(self):
@@ -136,9 +153,10 @@ class Workload:
             self.step_body()
 
     def launches_per_step(self):
-        # per layer: steady append, then the single decode kernel (RI_WAVE_STAGED=1: scan, select, attend)
+        # per layer: steady append, then the single decode kernel (RI_WAVE_STAGED=1: scan, select, attend),
+        # plus the flag wait of the peer-store gather
         staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")
-        return (4 if staged else 2) * self.geo.layers
+        return ((4 if staged else 2) + (1 if self.peer is not None else 0)) * self.geo.layers
 
     def static_len(self):
         return int(self.cache._per_device[str(self.device)]["static_len"].item())
@@ -339,10 +357,25 @@ def run_decode(geo, args, rank, world, local_rank, log):
     barrier()
     ms_e2e = e0.elapsed_time(e1)
 
+    gather_check = None
     if world > 1:
         t = torch.tensor([ms, ms_e2e])
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=cpu_group)
         ms, ms_e2e = t.tolist()
+        if wl.peer is not None:
+            # every rank's slice of the last step must have arrived in this rank's gather buffer: compare
+            # per-layer sums of the ranks' own outputs with the sums of the slices received
+            torch.cuda.synchronize()
+            mine = wl.out.float().sum(dim=tuple(range(1, wl.out.dim()))).cpu()
+            sums = [None] * world
+            dist.all_gather_object(sums, mine, group=cpu_group)
+            got = wl.peer.gathered.float().sum(dim=(2, 3, 4, 5)).cpu()
+            ok = not wl.peer.timed_out()
+            for slot, r in enumerate(wl.shard.head_group_ranks()):
+                ok = ok and bool(torch.allclose(got[:, slot], sums[r], rtol=1e-3, atol=1e-2))
+            flags = torch.tensor([1.0 if ok else 0.0])
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=cpu_group)
+            gather_check = "ok" if flags.item() == 1.0 else "MISMATCH"
 
     # ---- per-kernel time and roofline (separate eager pass, events around each launch) ----
     stage_ms, n_ret_rows, static_len = time_stages(wl, 2 * (warm + args.steps), stage_steps)
@@ -377,17 +410,21 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                f"centroids, {cfg.n_segment} segments, nprobe {cfg.nprobe}, estimate {wl.shape.n_estimate}",
                    "parallelism": (f"{world} ranks: {wl.shard.head_shards} KV-head shards x {wl.shard.batch_shards} batch "
                                    f"shards; per rank {lg.kv_heads} kv heads x batch {lg.batch} = {wl.shape.groups} groups; "
-                                   f"one NCCL all-gather of the head slices per layer") if world > 1 else "single GPU",
+                                   + ("head slices stored into every rank's gather buffer by the decode kernel "
+                                      "(peer stores over NVLink), one bounded flag wait per layer"
+                                      if wl.peer is not None else "one NCCL all-gather of the head slices per layer"))
+                                  if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (each layer-step touches its own ~110 MB; ~3.5 GB per step)",
                    "index": f"built by ri_kmeans_build during untimed set-up ({args.kmeans_iters} iterations, "
                             f"median {wl.prefill_index_ms:.1f} ms per request-layer incl. layout)",
+                   "gather_check": gather_check,
                    "graph": "one CUDA graph per decode step" if wl.graph is not None else
                             "eager stepping (capture failed: " + getattr(wl, "capture_error", "?") + ")"},
         "e2e": {"value": round(tokens / (ms_e2e / 1e3), 2), "unit": "tok/s",
                 "h2d_bytes_per_step": int(2 * (wl.q_in.numel() + wl.k_in.numel() + wl.v_in.numel())),
                 "d2h_bytes_per_step": int(2 * wl.out.numel())},
         "gpu_launches": wl.launches_per_step() * args.steps,
-        "nccl_collectives": (geo.layers * args.steps) if world > 1 else 0,
+        "nccl_collectives": (geo.layers * args.steps) if (world > 1 and wl.peer is None) else 0,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": kernels[top]["gbs"], "peak": peak,
                      "unit": "GB/s", "frac": kernels[top]["frac"], "peak_kind": "of " + peak_kind, "traffic": traffic,

@@ -32,6 +32,16 @@ class WaveLayer(C.Structure):
     ]
 
 
+class WaveGather(C.Structure):
+    """Mirror of ``struct ri_wave_gather``."""
+
+    _fields_ = [
+        ("n_ranks", C.c_int32), ("rank", C.c_int32),
+        ("d_out_slots", C.c_void_p), ("d_flag_slots", C.c_void_p), ("d_flags", C.c_void_p),
+        ("d_state", C.c_void_p), ("d_error", C.c_void_p), ("wait_limit_us", C.c_int32),
+    ]
+
+
 class KMeans(C.Structure):
     """Mirror of ``struct ri_kmeans``."""
 
@@ -67,6 +77,10 @@ def _load() -> C.CDLL:
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]
     lib.ri_wave_attend_buffer.restype = C.c_int
     lib.ri_wave_attend_buffer.argtypes = [C.POINTER(WaveLayer), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+    lib.ri_wave_decode_layer_gather.restype = C.c_int
+    lib.ri_wave_decode_layer_gather.argtypes = [C.POINTER(WaveLayer), C.POINTER(WaveGather), C.c_void_p]
+    lib.ri_wave_gather_wait.restype = C.c_int
+    lib.ri_wave_gather_wait.argtypes = [C.POINTER(WaveGather), C.c_void_p]
     lib.ri_wave_scratch_views.restype = C.c_int
     lib.ri_wave_scratch_views.argtypes = [C.POINTER(WaveLayer), C.POINTER(WaveViews)]
     lib.ri_kmeans_scratch_bytes.restype = C.c_int64

@@ -235,13 +235,18 @@ class retroinfer_cache(KV_Cache):
                 p["append_pos"].add_(1)
         return None, None
 
-    def compute(self, queries, layer_idx, queries_next=None, out=None):
+    def compute(self, queries, layer_idx, queries_next=None, out=None, gather=None):
         """Wave-index attention for one layer (:549-697).  queries: [batch, 1, heads, d].
-        ``out`` (optional, not in the reference) receives the result instead of a new tensor."""
+        ``out`` (optional, not in the reference) receives the result instead of a new tensor.
+        ``gather`` (optional, several GPUs): a ``head_shard.PeerGather``; the decode kernel then also
+        stores this rank's head slice into every rank's gather buffer (no collective afterwards)."""
         if self.kv_on_host:
+            if gather is not None:
+                raise NotImplementedError("the peer-store gather is built for the HBM tier only")
             out = self._compute_host_tier(queries.contiguous(), layer_idx, out)
         else:
-            out = self._layers[layer_idx].compute(queries.contiguous(), out)
+            out = self._layers[layer_idx].compute(queries.contiguous(), out,
+                                                  gather=None if gather is None else gather.params[layer_idx])
         if layer_idx == self.layer_num - 1:
             # every layer of a step attends static_pattern_total(+1) rows (:559); advance for the next step
             for p in self._per_device.values():

@@ -69,6 +69,8 @@ struct AttendArgs {
   int G, C, gs, E, e_pad, e_steps, steady_stride, max_rows;
   float scale2;        // log2(e) / sqrt(d)
   int cost_est, cost_exact;   // relative cost of an estimation / exact step when the steps are shared out
+  uint16_t* const* copies;    // device array of n_copies more destinations of the output (other GPUs' gather buffers)
+  int n_copies;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -414,7 +416,13 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
       L += lc[c] * f;
       O += oc[c] * f;
     }
-    reinterpret_cast<uint16_t*>(a.out)[((int64_t)g * gs + h) * RI_HEAD_DIM + ch] = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
+    const uint16_t bits = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
+    const int64_t idx = ((int64_t)g * gs + h) * RI_HEAD_DIM + ch;
+    reinterpret_cast<uint16_t*>(a.out)[idx] = bits;
+    if (a.n_copies > 0) {
+      for (int c = 0; c < a.n_copies; ++c) a.copies[c][idx] = bits;
+      __threadfence_system();   // ordered before the flag that the kernel's last CTA raises on those GPUs
+    }
   }
   cluster.sync();                        // remote reads done: the partials and the ring may be reused
 }
@@ -439,6 +447,8 @@ inline void fill_attend_args(const ri_wave_layer& p, const Layout& L, const Exec
   a.e_steps = (p.n_estimate + 15) / 16;
   a.steady_stride = p.steady_stride; a.max_rows = p.max_exact_rows;
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  a.copies = nullptr;
+  a.n_copies = 0;
   static const int cost_est = getenv("RI_COST_EST") ? atoi(getenv("RI_COST_EST")) : RI_COST_EST;
   static const int cost_exact = getenv("RI_COST_EXACT") ? atoi(getenv("RI_COST_EXACT")) : RI_COST_EXACT;
   a.cost_est = cost_est > 0 ? cost_est : 1;

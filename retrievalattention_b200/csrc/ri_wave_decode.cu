@@ -116,6 +116,31 @@ extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
   return launch_attend(*p, L, s);
 }
 
+namespace {
+int validate_gather(const ri_wave_gather* g) {
+  RI_REQUIRE(g != nullptr, "ri_wave_gather is null");
+  RI_REQUIRE(g->n_ranks >= 2 && g->n_ranks <= 64, "n_ranks=%d unsupported (2..64)", g->n_ranks);
+  RI_REQUIRE(g->rank >= 0 && g->rank < g->n_ranks, "rank=%d outside the group of %d", g->rank, g->n_ranks);
+  RI_REQUIRE(g->d_out_slots && g->d_flag_slots && g->d_flags && g->d_state && g->d_error, "ri_wave_gather: null pointer");
+  return RI_OK;
+}
+}  // namespace
+
+extern "C" int ri_wave_decode_layer_gather(const ri_wave_layer* p, const ri_wave_gather* g, void* stream) {
+  int rc = validate(p);
+  if (rc != RI_OK) return rc;
+  if ((rc = validate_gather(g)) != RI_OK) return rc;
+  RI_REQUIRE(fused_supported(*p), "the gather form needs the single decode kernel (n_centroids=%d too large)", p->n_centroids);
+  const Layout L = make_layout(*p);
+  return launch_fused(*p, L, static_cast<cudaStream_t>(stream), g);
+}
+
+extern "C" int ri_wave_gather_wait(const ri_wave_gather* g, void* stream) {
+  const int rc = validate_gather(g);
+  if (rc != RI_OK) return rc;
+  return launch_gather_wait(*g, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ri_steady_append(const void* d_k, const void* d_v, void* d_steady_keys, void* d_steady_values,
                                 const int32_t* d_position, int32_t groups, int32_t steady_stride, void* stream) {
   RI_REQUIRE(d_k && d_v && d_steady_keys && d_steady_values && d_position, "ri_steady_append: null pointer");

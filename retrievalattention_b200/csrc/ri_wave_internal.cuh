@@ -66,7 +66,8 @@ int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
 int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr);
 // scan + select + attend as one kernel (one 8-CTA cluster per group).
-int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
+int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather = nullptr);
+int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s);
 bool fused_supported(const ri_wave_layer& p);   // geometries the single kernel covers (others run the three stages)
 
 }  // namespace ri_wave

@@ -107,3 +107,79 @@ class HeadGather:
         else:
             dist.all_gather_into_tensor(gathered.view(-1), out_local.contiguous().view(-1), group=self.group)
         return gathered.permute(1, 2, 0, 3, 4).reshape(b, one, s.head_shards * hl, d)
+
+
+class PeerGather:
+    """The same gather without a collective: every rank's decode kernel stores its head slice straight
+    into the gather buffer of every rank of its group (peer-mapped memory over NVLink) and raises a
+    flag there when its last CTA is done; ``wait(layer)`` enqueues a one-warp kernel that waits — with
+    a time limit — until all flags of that layer have reached the current step.
+
+    Buffers come from ``torch.distributed._symmetric_memory`` (one allocation per rank, mapped into
+    every rank of ``group``).  NVLink multicast is not used (plain peer stores), and it is switched off
+    for the allocation so that no rank's memory is bound to a multicast object.
+
+    Layout per rank: ``gathered[layer, shard, B, 1, Hq_local, d]`` and ``flags[layer, shard]``;
+    ``view(layer)`` returns the ``[B, 1, Hq, d]`` view of a layer's gathered output.
+    """
+
+    def __init__(self, shard: HeadShard, layers: int, batch: int, q_heads_local: int, head_dim: int,
+                 dtype: torch.dtype, device: torch.device, group=None, wait_limit_us: int = 0):
+        import ctypes as C
+        import os
+
+        from . import _lib
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.shard, self.layers = shard, layers
+        n = shard.head_shards
+        me = shard.head_index
+        group = group if group is not None else dist.group.WORLD
+        slice_elems = batch * q_heads_local * head_dim
+        self.gathered = symm_mem.empty((layers, n, batch, 1, q_heads_local, head_dim), dtype=dtype, device=device)
+        self.flags = symm_mem.empty((layers, n), dtype=torch.int32, device=device)
+        self.gathered.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        h_out = symm_mem.rendezvous(self.gathered, group)
+        h_flag = symm_mem.rendezvous(self.flags, group)
+        if h_out.world_size != n or h_out.rank != me:
+            raise RuntimeError("PeerGather: the process group does not match the head shards")
+        self.state = torch.zeros((layers, 4), dtype=torch.int32, device=device)
+        self.error = torch.zeros((1,), dtype=torch.int32, device=device)
+        esz = self.gathered.element_size()
+        out_slots = torch.tensor([[h_out.buffer_ptrs[p] + (l * n + me) * slice_elems * esz for p in range(n)]
+                                  for l in range(layers)], dtype=torch.int64)
+        flag_slots = torch.tensor([[h_flag.buffer_ptrs[p] + (l * n + me) * 4 for p in range(n)]
+                                   for l in range(layers)], dtype=torch.int64)
+        self._out_slots = out_slots.to(device)
+        self._flag_slots = flag_slots.to(device)
+        self._handles = (h_out, h_flag)          # keep the mappings alive
+        self.params = []
+        for l in range(layers):
+            g = _lib.WaveGather()
+            g.n_ranks, g.rank = n, me
+            g.d_out_slots = self._out_slots[l].data_ptr()
+            g.d_flag_slots = self._flag_slots[l].data_ptr()
+            g.d_flags = self.flags[l].data_ptr()
+            g.d_state = self.state[l].data_ptr()
+            g.d_error = self.error.data_ptr()
+            g.wait_limit_us = wait_limit_us
+            self.params.append(g)
+        self._C, self._lib = C, _lib
+        torch.cuda.synchronize(device)
+
+    def wait(self, layer: int) -> None:
+        """Enqueue the bounded wait for ``layer``'s slices of this step on the current stream."""
+        self._lib.check(self._lib.lib.ri_wave_gather_wait(self._C.byref(self.params[layer]), self._lib.current_stream()),
+                        "ri_wave_gather_wait")
+
+    def view(self, layer: int) -> torch.Tensor:
+        n, b, one, hl, d = self.gathered.shape[1:]
+        return self.gathered[layer].permute(1, 2, 0, 3, 4).reshape(b, one, n * hl, d)
+
+    def timed_out(self) -> bool:
+        """True when some wait gave up (reads one word from the device)."""
+        return bool(self.error.item())

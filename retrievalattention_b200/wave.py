@@ -109,12 +109,18 @@ class WaveIndexLayer:
         assert out.is_cuda and out.is_contiguous() and out.dtype == s.dtype and out.numel() == q.numel()
         self.params.d_q, self.params.d_out = q.data_ptr(), out.data_ptr()
 
-    def compute(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """scan + select + attend (one kernel) on the current stream.  ``q``: [B, 1, Hq, 128] (or [G, gs, 128])."""
+    def compute(self, q: torch.Tensor, out: torch.Tensor | None = None, gather=None) -> torch.Tensor:
+        """scan + select + attend (one kernel) on the current stream.  ``q``: [B, 1, Hq, 128] (or [G, gs, 128]).
+        ``gather`` (a ``_lib.WaveGather``): the kernel also stores the output into every rank's gather
+        buffer and raises this rank's flags there (several GPUs, see ``head_shard.PeerGather``)."""
         if out is None:
             out = torch.empty_like(q)
         self._bind(q, out)
-        _lib.check(_lib.lib.ri_wave_decode_layer(C.byref(self.params), _lib.current_stream()), "ri_wave_decode_layer")
+        if gather is None:
+            _lib.check(_lib.lib.ri_wave_decode_layer(C.byref(self.params), _lib.current_stream()), "ri_wave_decode_layer")
+        else:
+            _lib.check(_lib.lib.ri_wave_decode_layer_gather(C.byref(self.params), C.byref(gather), _lib.current_stream()),
+                       "ri_wave_decode_layer_gather")
         return out
 
     def compute_staged(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
