@@ -107,7 +107,7 @@ class Workload:
                 try:
                     from retrievalattention_b200.head_shard import PeerGather
                     self.peer = PeerGather(self.shard, geo.layers, geo.batch, geo.q_heads, geo.head_dim, torch.bfloat16,
-                                           device, group=self.gather.group)
+                                           device, groups=geo.batch * geo.kv_heads, group=self.gather.group)
                 except Exception as exc:     # noqa: BLE001 — any set-up failure falls back to the collective
                     self.peer_error = repr(exc)[:200]
                     if log:
@@ -123,6 +123,8 @@ class Workload:
         Several GPUs: the head slices of all ranks -> [B, 1, Hq, d] for the output projection, either
         written by the decode kernel into every rank's buffer (then one bounded flag wait per layer) or
         by an NCCL all-gather."""
+        if self.peer is not None:
+            self.peer.next_step()
         for l in range(self.geo.layers):
             self.cache.decode_update_kv_cache(self.k_in[l], self.v_in[l], l)
             self.cache.compute(self.q_in[l], l, out=self.out[l], gather=self.peer)

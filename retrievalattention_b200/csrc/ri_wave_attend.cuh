@@ -419,10 +419,7 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
     const uint16_t bits = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
     const int64_t idx = ((int64_t)g * gs + h) * RI_HEAD_DIM + ch;
     reinterpret_cast<uint16_t*>(a.out)[idx] = bits;
-    if (a.n_copies > 0) {
-      for (int c = 0; c < a.n_copies; ++c) a.copies[c][idx] = bits;
-      __threadfence_system();   // ordered before the flag that the kernel's last CTA raises on those GPUs
-    }
+    for (int c = 0; c < a.n_copies; ++c) a.copies[c][idx] = bits;   // several GPUs: the other ranks' gather buffers
   }
   cluster.sync();                        // remote reads done: the partials and the ring may be reused
 }

@@ -31,10 +31,10 @@ struct FusedArgs {
   float* scores;     // global copy of the scores (a view for tests), written only when `views`
   float alpha;
   int views;         // also fill the global lists and views (tests, callers that asked for the id outputs)
-  // several GPUs: the flags this rank raises on every rank of its gather group once all its CTAs have stored
-  // their outputs there (att.copies); null when there is no gather
+  // several GPUs: this rank's row of flag words on every rank of its gather group (one word per CTA), raised
+  // once the CTA's outputs are stored there (att.copies); null when there is no gather
   uint32_t* const* flag_slots;
-  uint32_t* gather_state;   // [0] CTA ticket, [1] epochs sent
+  const uint32_t* epoch;
   int n_ranks;
   int persist_off;   // byte offset, behind the ring and the scores, of the lists that outlive the selection
   int cap;           // estimation entries a CTA can keep in shared memory (multiple of 16)
@@ -612,53 +612,39 @@ wave_fused_kernel(FusedArgs f) {
   else attend_group<DT, false>(f.att, g, rank, ring);
   RI_FT(13);
 
-  // ---- several GPUs: the last CTA of the grid raises this rank's flag on every rank of the group ----
-  // Every storing thread fenced its stores to the other GPUs (system scope) before the cluster barrier that ends
-  // the attend phase; the ticket below is taken after that barrier, so the CTA that draws the last ticket
-  // knows all stores of the grid are ordered before its flag writes.  Nothing here waits.
+  // ---- several GPUs: this CTA's outputs are stored on every rank (before the cluster barrier that ends the attend
+  //      phase): one system-scope fence, then the step's epoch into this CTA's flag word on every rank ----
   if (f.flag_slots != nullptr && tid == 0) {
-    __threadfence();
-    const unsigned total = gridDim.x * gridDim.y;
-    const unsigned ticket = atomicAdd(f.gather_state, 1u);
-    if (ticket == total - 1) {
-      __threadfence();
-      f.gather_state[0] = 0;                       // ready for the next launch on this stream
-      const uint32_t epoch = f.gather_state[1] + 1;
-      f.gather_state[1] = epoch;
-      __threadfence_system();
-      for (int p = 0; p < f.n_ranks; ++p)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flag_slots[p]), "r"(epoch) : "memory");
-    }
+    const uint32_t epoch = *f.epoch;
+    const int word = blockIdx.y * gridDim.x + blockIdx.x;
+    __threadfence_system();
+    for (int p = 0; p < f.n_ranks; ++p)
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f.flag_slots[p] + word), "r"(epoch) : "memory");
   }
 }
 
-// One warp waits (bounded) until every rank's flag of this layer has reached this step's epoch.
-__global__ void gather_wait_kernel(const uint32_t* flags, uint32_t* state, int32_t* error, int n_ranks, long long limit_ns) {
+// Waits (bounded) until every flag word of every rank of this layer holds this step's epoch.
+__global__ void gather_wait_kernel(const uint32_t* flags, const uint32_t* epoch, int32_t* error, int n_words,
+                                   long long limit_ns) {
   ri_pdl_enter();
-  const int lane = threadIdx.x;
-  const uint32_t expected = state[2] + 1;
+  const uint32_t expected = *epoch;
   unsigned long long t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   bool ok = true;
-  for (int r = lane; r < n_ranks; r += 32) {
-    uint32_t v;
+  for (int i = threadIdx.x; i < n_words && ok; i += blockDim.x) {
     long long spins = 0;
     for (;;) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
       if ((int32_t)(v - expected) >= 0) break;
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
       if ((long long)(now - t0) > limit_ns || ++spins > (1ll << 26)) { ok = false; break; }   // give up: time or count
-      __nanosleep(100);
+      __nanosleep(64);
     }
   }
-  ok = __all_sync(0xffffffffu, ok);
-  if (lane == 0) {
-    state[2] = expected;          // stays in step with the senders even after a failed wait
-    if (!ok) *error = 1;
-  }
+  if (!ok) *error = 1;
 }
-
 
 // Shared memory one CTA may use when two of them share an SM, minus the kernel's static part.
 template <int DT>
@@ -693,13 +679,15 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wav
   f.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(p.d_scratch) + L.scores);
   f.alpha = 0.08838834764831845f;
   f.views = p.d_retrieved_ids != nullptr;
-  f.flag_slots = nullptr; f.gather_state = nullptr; f.n_ranks = 0;
+  f.flag_slots = nullptr; f.epoch = nullptr; f.n_ranks = 0;
   if (gather) {
     f.att.copies = reinterpret_cast<uint16_t* const*>(gather->d_out_slots);
     f.att.n_copies = gather->n_ranks;
     f.flag_slots = gather->d_flag_slots;
-    f.gather_state = gather->d_state;
+    f.epoch = gather->d_epoch;
     f.n_ranks = gather->n_ranks;
+    RI_REQUIRE(gather->n_flags == kSelectCluster * p.groups, "n_flags=%d, the decode kernel has %d CTAs", gather->n_flags,
+               kSelectCluster * p.groups);
   }
   RI_REQUIRE(fused_supported(p), "the single-kernel path needs n_centroids <= %d", kMaxSlice * kSelectCluster);
   RI_REQUIRE((size_t)f.sel.p_pad * 44 <= (size_t)kScoreOffset, "nprobe=%d too large", p.nprobe);
@@ -739,7 +727,9 @@ int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const 
 
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s) {
   const long long limit_ns = (g.wait_limit_us > 0 ? (long long)g.wait_limit_us : 1000000ll) * 1000ll;
-  RI_CUDA_OK(ri_launch_pdl_id(6, gather_wait_kernel, dim3(1), dim3(32), 0, s, g.d_flags, g.d_state, g.d_error, g.n_ranks, limit_ns));
+  const int n_words = g.n_ranks * g.n_flags;
+  const int threads = n_words < 1024 ? ((n_words + 31) / 32) * 32 : 1024;
+  RI_CUDA_OK(ri_launch_pdl_id(6, gather_wait_kernel, dim3(1), dim3(threads), 0, s, g.d_flags, g.d_epoch, g.d_error, n_words, limit_ns));
   return RI_OK;
 }
 

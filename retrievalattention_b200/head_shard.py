@@ -111,20 +111,21 @@ class HeadGather:
 
 class PeerGather:
     """The same gather without a collective: every rank's decode kernel stores its head slice straight
-    into the gather buffer of every rank of its group (peer-mapped memory over NVLink) and raises a
-    flag there when its last CTA is done; ``wait(layer)`` enqueues a one-warp kernel that waits — with
-    a time limit — until all flags of that layer have reached the current step.
+    into the gather buffer of every rank of its group (peer-mapped memory over NVLink), and each of its
+    CTAs then writes the step's epoch into its flag word on every rank; ``wait(layer)`` enqueues a small
+    kernel that waits — with a time limit — until all flag words of that layer hold the epoch.
 
     Buffers come from ``torch.distributed._symmetric_memory`` (one allocation per rank, mapped into
     every rank of ``group``).  NVLink multicast is not used (plain peer stores), and it is switched off
     for the allocation so that no rank's memory is bound to a multicast object.
 
-    Layout per rank: ``gathered[layer, shard, B, 1, Hq_local, d]`` and ``flags[layer, shard]``;
-    ``view(layer)`` returns the ``[B, 1, Hq, d]`` view of a layer's gathered output.
+    Per step: ``next_step()`` once (advances the epoch), then per layer ``compute(..., gather=self)``
+    and ``wait(layer)``.  Layout per rank: ``gathered[layer, shard, B, 1, Hq_local, d]`` and
+    ``flags[layer, shard, 8 * groups]``; ``view(layer)`` is the ``[B, 1, Hq, d]`` view of a layer.
     """
 
     def __init__(self, shard: HeadShard, layers: int, batch: int, q_heads_local: int, head_dim: int,
-                 dtype: torch.dtype, device: torch.device, group=None, wait_limit_us: int = 0):
+                 dtype: torch.dtype, device: torch.device, groups: int, group=None, wait_limit_us: int = 0):
         import ctypes as C
         import os
 
@@ -136,10 +137,11 @@ class PeerGather:
         self.shard, self.layers = shard, layers
         n = shard.head_shards
         me = shard.head_index
+        n_flags = 8 * groups                      # CTAs of the decode kernel
         group = group if group is not None else dist.group.WORLD
         slice_elems = batch * q_heads_local * head_dim
         self.gathered = symm_mem.empty((layers, n, batch, 1, q_heads_local, head_dim), dtype=dtype, device=device)
-        self.flags = symm_mem.empty((layers, n), dtype=torch.int32, device=device)
+        self.flags = symm_mem.empty((layers, n, n_flags), dtype=torch.int32, device=device)
         self.gathered.zero_()
         self.flags.zero_()
         torch.cuda.synchronize(device)
@@ -147,12 +149,12 @@ class PeerGather:
         h_flag = symm_mem.rendezvous(self.flags, group)
         if h_out.world_size != n or h_out.rank != me:
             raise RuntimeError("PeerGather: the process group does not match the head shards")
-        self.state = torch.zeros((layers, 4), dtype=torch.int32, device=device)
+        self.epoch = torch.zeros((1,), dtype=torch.int32, device=device)
         self.error = torch.zeros((1,), dtype=torch.int32, device=device)
         esz = self.gathered.element_size()
         out_slots = torch.tensor([[h_out.buffer_ptrs[p] + (l * n + me) * slice_elems * esz for p in range(n)]
                                   for l in range(layers)], dtype=torch.int64)
-        flag_slots = torch.tensor([[h_flag.buffer_ptrs[p] + (l * n + me) * 4 for p in range(n)]
+        flag_slots = torch.tensor([[h_flag.buffer_ptrs[p] + (l * n + me) * n_flags * 4 for p in range(n)]
                                    for l in range(layers)], dtype=torch.int64)
         self._out_slots = out_slots.to(device)
         self._flag_slots = flag_slots.to(device)
@@ -160,16 +162,19 @@ class PeerGather:
         self.params = []
         for l in range(layers):
             g = _lib.WaveGather()
-            g.n_ranks, g.rank = n, me
+            g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = n, me, n_flags, wait_limit_us
             g.d_out_slots = self._out_slots[l].data_ptr()
             g.d_flag_slots = self._flag_slots[l].data_ptr()
             g.d_flags = self.flags[l].data_ptr()
-            g.d_state = self.state[l].data_ptr()
+            g.d_epoch = self.epoch.data_ptr()
             g.d_error = self.error.data_ptr()
-            g.wait_limit_us = wait_limit_us
             self.params.append(g)
         self._C, self._lib = C, _lib
         torch.cuda.synchronize(device)
+
+    def next_step(self) -> None:
+        """Advance the epoch (enqueued on the current stream): once per decode step, on every rank."""
+        self.epoch.add_(1)
 
     def wait(self, layer: int) -> None:
         """Enqueue the bounded wait for ``layer``'s slices of this step on the current stream."""

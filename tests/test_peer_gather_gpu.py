@@ -18,17 +18,16 @@ pytestmark = pytest.mark.gpu
 CASE = Case(2, 2, 4, 2048 + 68, 128, 1, 6, 30, seed=11)
 
 
-def make_gather(rank, n, out_bufs, flag_bufs, state, error, limit_us, keep):
+def make_gather(rank, n, n_flags, out_bufs, flag_bufs, epoch, error, limit_us, keep):
     slice_bytes = out_bufs[0][0].numel() * out_bufs[0].element_size()
     out_slots = torch.tensor([b.data_ptr() + rank * slice_bytes for b in out_bufs], dtype=torch.int64).cuda()
-    flag_slots = torch.tensor([f.data_ptr() + rank * 4 for f in flag_bufs], dtype=torch.int64).cuda()
+    flag_slots = torch.tensor([f.data_ptr() + rank * n_flags * 4 for f in flag_bufs], dtype=torch.int64).cuda()
     keep += [out_slots, flag_slots]
     g = _lib.WaveGather()
-    g.n_ranks, g.rank = n, rank
+    g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = n, rank, n_flags, limit_us
     g.d_out_slots, g.d_flag_slots = out_slots.data_ptr(), flag_slots.data_ptr()
     g.d_flags = flag_bufs[rank].data_ptr()
-    g.d_state, g.d_error = state[rank].data_ptr(), error.data_ptr()
-    g.wait_limit_us = limit_us
+    g.d_epoch, g.d_error = epoch.data_ptr(), error.data_ptr()
     return g
 
 
@@ -37,13 +36,15 @@ def test_two_ranks_on_one_gpu_fill_both_buffers_and_the_wait_returns():
     layers = [to_gpu_layer(CASE, cpu, SINK + RECENT, want_ids=False) for _ in range(2)]
     qs = [queries(CASE).cuda(), (queries(CASE) * 0.5).to(torch.bfloat16).cuda()]
     g_, gs = CASE.groups, CASE.group_size
+    n_flags = 8 * g_
     out_bufs = [torch.zeros((2, g_, gs, 128), dtype=torch.bfloat16, device="cuda") for _ in range(2)]   # per "rank"
-    flag_bufs = [torch.zeros((2,), dtype=torch.int32, device="cuda") for _ in range(2)]
-    state = torch.zeros((2, 4), dtype=torch.int32, device="cuda")
+    flag_bufs = [torch.zeros((2, n_flags), dtype=torch.int32, device="cuda") for _ in range(2)]
+    epoch = torch.zeros((1,), dtype=torch.int32, device="cuda")
     error = torch.zeros((1,), dtype=torch.int32, device="cuda")
     keep = []
-    gathers = [make_gather(r, 2, out_bufs, flag_bufs, state, error, 200000, keep) for r in range(2)]
-    for step in range(3):                       # epochs advance with the calls
+    gathers = [make_gather(r, 2, n_flags, out_bufs, flag_bufs, epoch, error, 200000, keep) for r in range(2)]
+    for step in range(3):
+        epoch.add_(1)
         outs = [layers[r].compute(qs[r], gather=gathers[r]).clone() for r in range(2)]
         for r in range(2):
             _lib.check(_lib.lib.ri_wave_gather_wait(C.byref(gathers[r]), _lib.current_stream()))
@@ -52,22 +53,22 @@ def test_two_ranks_on_one_gpu_fill_both_buffers_and_the_wait_returns():
         for buf in out_bufs:                    # every rank's buffer holds both slices
             for r in range(2):
                 assert torch.equal(buf[r].view(torch.int16), outs[r].reshape(g_, gs, 128).view(torch.int16))
-        assert flag_bufs[0].tolist() == [step + 1, step + 1] and flag_bufs[1].tolist() == [step + 1, step + 1]
+        for f in flag_bufs:
+            assert (f == step + 1).all()
     plain = layers[0].compute(qs[0])            # the gather form computes what the plain form computes
     torch.cuda.synchronize()
     assert torch.equal(plain.view(torch.int16), outs[0].view(torch.int16))
 
 
 def test_wait_gives_up_after_its_limit_and_reports_it():
-    flags = torch.zeros((2,), dtype=torch.int32, device="cuda")     # nothing ever raises these
-    state = torch.zeros((1, 4), dtype=torch.int32, device="cuda")
+    flags = torch.zeros((2, 16), dtype=torch.int32, device="cuda")     # nothing ever raises these
+    epoch = torch.ones((1,), dtype=torch.int32, device="cuda")
     error = torch.zeros((1,), dtype=torch.int32, device="cuda")
     dummy = torch.zeros((2,), dtype=torch.int64, device="cuda")
     g = _lib.WaveGather()
-    g.n_ranks, g.rank = 2, 0
+    g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = 2, 0, 16, 2000
     g.d_out_slots = g.d_flag_slots = dummy.data_ptr()
-    g.d_flags, g.d_state, g.d_error = flags.data_ptr(), state.data_ptr(), error.data_ptr()
-    g.wait_limit_us = 2000
+    g.d_flags, g.d_epoch, g.d_error = flags.data_ptr(), epoch.data_ptr(), error.data_ptr()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     _lib.check(_lib.lib.ri_wave_gather_wait(C.byref(g), _lib.current_stream()))
@@ -75,13 +76,12 @@ def test_wait_gives_up_after_its_limit_and_reports_it():
     torch.cuda.synchronize()
     assert int(error.item()) == 1
     assert 1.0 <= a.elapsed_time(b) < 200.0     # about the 2 ms limit, and the context is still usable
-    assert int(state[0, 2].item()) == 1         # the epoch advanced all the same
     assert torch.zeros(4, device="cuda").sum().item() == 0.0
 
 
 def test_invalid_gather_arguments_are_rejected():
     g = _lib.WaveGather()
-    g.n_ranks, g.rank = 1, 0
+    g.n_ranks, g.rank, g.n_flags = 1, 0, 8
     assert _lib.lib.ri_wave_gather_wait(C.byref(g), None) != 0
     g.n_ranks, g.rank = 2, 5
     assert _lib.lib.ri_wave_gather_wait(C.byref(g), None) != 0
