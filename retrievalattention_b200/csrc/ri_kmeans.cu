@@ -108,6 +108,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// tcgen05.ld fills its destination registers asynchronously, and nothing tells the compiler that their
+// readers must stay behind tcgen05.wait::ld.  Passing the registers through an empty volatile asm after the
+// wait does: volatile asms keep their order, and every later use now depends on this one.
+__device__ __forceinline__ void tc_ld_landed(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]));
+}
 
 // K-major operand tile, 128-byte swizzle: rows of 128 B (64 channels), 8-row atoms 1024 B apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -238,6 +248,7 @@ kmeans_assign_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_
         uint32_t r[32];
         tc_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * kTileN + ch * 32, r);
         tc_wait_ld();
+        tc_ld_landed(r);
         if (ch * 32 + 32 <= valid) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -266,6 +277,237 @@ kmeans_assign_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+// ---- assign, wide form ----------------------------------------------------------------------------
+// The form the build uses: a CTA works through consecutive 256-token blocks of one problem.  Per block
+// two 128-row token tiles (A, double-buffered per block) meet every centroid tile (B, streamed
+// through three stages) in two MMAs, so a centroid tile fetched into shared memory serves 256 tokens
+// and the CTA's set-up is paid once for many blocks; the accumulators fill all 512 TMEM columns
+// (2 buffers x 2 token tiles x 128 centroids).  Ten warps: TMA producer, MMA issuer, and eight
+// epilogue warps (four per token tile, one per TMEM lane quarter) that keep the running arg-max
+// of their 32 tokens: per 32 columns a max tree, then the first column equal to the max (ties ->
+// lowest index, the rule of torch.argmax), so nothing in the epilogue is a serial chain.
+// Every mbarrier wait is bounded as in the narrow form above.
+constexpr int kWideThreads = 320;
+constexpr int kWideBStages = 3;
+constexpr uint32_t kWideTmemCols = 512;
+constexpr int kWideSmem = 1024 /*align*/ + 2 * 4 * kHalfBytes /*A: 2 blocks x 2 tiles*/ +
+                          kWideBStages * 2 * kHalfBytes /*B*/ + 256 /*barriers*/;
+
+struct WideArgs {
+  AssignArgs a;
+  int blocks_per_cta;    // 256-token blocks a CTA works through
+};
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));   // three-input maximum (sm_100)
+  return d;
+}
+
+// arg-max of 32 accumulator columns against the running (best, best_idx).  FULL: all 32 columns exist.
+template <bool FULL>
+__device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int col_base, int valid, float& best, int& best_idx) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = FULL || i < valid ? __uint_as_float(r[i]) : -INFINITY;
+  float m11[11];
+#pragma unroll
+  for (int i = 0; i < 10; ++i) m11[i] = max3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+  m11[10] = fmaxf(v[30], v[31]);
+  const float a0 = max3(m11[0], m11[1], m11[2]), a1 = max3(m11[3], m11[4], m11[5]), a2 = max3(m11[6], m11[7], m11[8]);
+  const float m = max3(max3(a0, a1, a2), m11[9], m11[10]);
+  if (m > best) {          // strict: an equal value in a later column never replaces an earlier one
+    uint32_t mask = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) mask |= (v[i] == m ? 1u : 0u) << i;
+    best = m;
+    best_idx = col_base + __ffs((int)mask) - 1;
+  }
+}
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+kmeans_assign_wide_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_constant__ CUtensorMap map_cent,
+                          WideArgs w) {
+  const AssignArgs& a = w.a;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // SW128 tiles need 1024-byte alignment
+  const uint32_t sA = base;                                         // [block parity][tile][K half]
+  const uint32_t sB = base + 2 * 4 * kHalfBytes;                    // [stage][K half]
+  const uint32_t bars = sB + kWideBStages * 2 * kHalfBytes;
+  auto bar_a_full = [&](int s) { return bars + 8u * s; };
+  auto bar_a_empty = [&](int s) { return bars + 8u * (2 + s); };
+  auto bar_b_full = [&](int s) { return bars + 8u * (4 + s); };
+  auto bar_b_empty = [&](int s) { return bars + 8u * (4 + kWideBStages + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (4 + 2 * kWideBStages + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (6 + 2 * kWideBStages + b); };
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort, s_skip;
+
+  // once any CTA of this launch has given up, the rest leave at once (uniformly per CTA)
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(a.error_flag);
+  __syncthreads();
+  if (s_skip) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int problem = blockIdx.y;
+  const int n_blocks_total = (a.n_tok + 2 * kTileM - 1) / (2 * kTileM);
+  const int first_block = blockIdx.x * w.blocks_per_cta;
+  const int nb = min(w.blocks_per_cta, n_blocks_total - first_block);       // > 0 by the grid's construction
+  const int64_t tok_row0 = (int64_t)(problem / a.seg_per_group) * a.group_stride +
+                           (int64_t)(problem % a.seg_per_group) * a.n_tok + (int64_t)first_block * 2 * kTileM;
+  const int cen_row0 = problem * a.n_cen;
+  const int n_tiles = (a.n_cen + kTileN - 1) / kTileN;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_a_full(s), 1); mbar_init(bar_a_empty(s), 1); }
+    for (int s = 0; s < kWideBStages; ++s) { mbar_init(bar_b_full(s), 1); mbar_init(bar_b_empty(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(kWideTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int a_issued = 0, b_issued = 0;
+      auto load_a = [&](int blk) {          // both token tiles of a block: 4 boxes of 128 rows x 64 channels
+        const int sa = blk & 1;
+        if (!mbar_wait(bar_a_empty(sa), ((blk >> 1) & 1) ^ 1, abort_flag, 11)) return false;
+        mbar_arrive_expect_tx(bar_a_full(sa), 4 * kHalfBytes);
+        const int row = (int)(tok_row0 + (int64_t)blk * 2 * kTileM);
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile) {
+          tma_load_2d(sA + (sa * 4 + tile * 2) * kHalfBytes, &map_keys, bar_a_full(sa), 0, row + tile * kTileM);
+          tma_load_2d(sA + (sa * 4 + tile * 2 + 1) * kHalfBytes, &map_keys, bar_a_full(sa), 64, row + tile * kTileM);
+        }
+        a_issued = blk + 1;
+        return true;
+      };
+      bool ok = load_a(0);
+      for (int blk = 0; ok && blk < nb; ++blk) {
+        for (int t = 0; ok && t < n_tiles; ++t) {
+          const int s = b_issued % kWideBStages;
+          ok = mbar_wait(bar_b_empty(s), ((b_issued / kWideBStages) & 1) ^ 1, abort_flag, 12);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_b_full(s), 2 * kHalfBytes);
+          tma_load_2d(sB + s * 2 * kHalfBytes, &map_cent, bar_b_full(s), 0, cen_row0 + t * kTileN);
+          tma_load_2d(sB + s * 2 * kHalfBytes + kHalfBytes, &map_cent, bar_b_full(s), 64, cen_row0 + t * kTileN);
+          ++b_issued;
+          if (t == 0 && blk + 1 < nb) ok = load_a(blk + 1);   // the next block's tokens, well ahead of their use
+        }
+      }
+      if (*abort_flag) {
+        // give our own copies still in flight a bounded chance to land before the CTA exits
+        for (int blk = max(0, a_issued - 2); blk < a_issued; ++blk)
+          mbar_wait(bar_a_full(blk & 1), (blk >> 1) & 1, abort_flag, 16);
+        for (int j = max(0, b_issued - kWideBStages); j < b_issued; ++j)
+          mbar_wait(bar_b_full(j % kWideBStages), (j / kWideBStages) & 1, abort_flag, 17);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int j = 0;                       // centroid tiles issued so far (accumulator buffer = j & 1, B stage = j % 3)
+      bool ok = true;
+      for (int blk = 0; ok && blk < nb; ++blk) {
+        const int sa = blk & 1;
+        ok = mbar_wait(bar_a_full(sa), (blk >> 1) & 1, abort_flag, 13);
+        for (int t = 0; ok && t < n_tiles; ++t, ++j) {
+          const int s = j % kWideBStages, buf = j & 1;
+          ok = mbar_wait(bar_b_full(s), (j / kWideBStages) & 1, abort_flag, 14) &&
+               mbar_wait(bar_acc_empty(buf), ((j >> 1) & 1) ^ 1, abort_flag, 15);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int tile = 0; tile < 2; ++tile) {
+            const uint32_t d_tmem = tmem_base + buf * 2 * kTileN + tile * kTileN;
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint64_t da = umma_desc_sw128(sA + (sa * 4 + tile * 2 + kb) * kHalfBytes);
+              const uint64_t db = umma_desc_sw128(sB + s * 2 * kHalfBytes + kb * kHalfBytes);
+#pragma unroll
+              for (int k = 0; k < 4; ++k)   // K16 steps: 32 bytes along the swizzled row = +2 in the address field
+                tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, a.idesc, (kb | k) != 0);
+            }
+          }
+          tc_commit(bar_b_empty(s));     // the stage is free once these MMAs have read it
+          tc_commit(bar_acc_full(buf));  // and both accumulators of the buffer are complete
+        }
+        if (ok) tc_commit(bar_a_empty(sa));   // the block's token tiles are free once all its MMAs have read them
+      }
+    }
+  } else {
+    // ---------------- epilogue: running arg-max over the centroid tiles ----------------
+    const int tile = (warp - 2) >> 2;                // which token tile of the block
+    const int lane_group = warp & 3;                 // TMEM lanes 32*lane_group .. +31 (a warp may touch only its quarter)
+    int j = 0;
+    bool ok = true;
+    for (int blk = 0; ok && blk < nb; ++blk) {
+      float best = -INFINITY;
+      int best_idx = 0;
+      for (int t = 0; ok && t < n_tiles; ++t, ++j) {
+        const int buf = j & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(buf), (j >> 1) & 1, abort_flag, 18));   // warp-uniform
+        if (!ok) break;
+        tc_fence_after();
+        const int col0 = t * kTileN;
+        const int valid = min(kTileN, a.n_cen - col0);
+        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 2 * kTileN + tile * kTileN;
+        // the second half of the columns is on its way from TMEM while the first is being reduced
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tc_ld32(taddr, r0);
+        tc_ld32(taddr + 32, r1);
+        tc_wait_ld();
+        tc_ld_landed(r0);
+        tc_ld_landed(r1);
+        tc_ld32(taddr + 64, r2);
+        tc_ld32(taddr + 96, r3);
+        if (valid == kTileN) {
+          argmax32<true>(r0, col0, 32, best, best_idx);
+          argmax32<true>(r1, col0 + 32, 32, best, best_idx);
+          tc_wait_ld();
+          tc_ld_landed(r2);
+          tc_ld_landed(r3);
+          argmax32<true>(r2, col0 + 64, 32, best, best_idx);
+          argmax32<true>(r3, col0 + 96, 32, best, best_idx);
+        } else {
+          argmax32<false>(r0, col0, valid, best, best_idx);
+          argmax32<false>(r1, col0 + 32, valid - 32, best, best_idx);
+          tc_wait_ld();
+          tc_ld_landed(r2);
+          tc_ld_landed(r3);
+          argmax32<false>(r2, col0 + 64, valid - 64, best, best_idx);
+          argmax32<false>(r3, col0 + 96, valid - 96, best, best_idx);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+      }
+      const int local_tok = (first_block + blk) * 2 * kTileM + tile * kTileM + lane_group * 32 + lane;
+      if (ok && local_tok < a.n_tok)
+        a.assign[tok_row0 + (int64_t)blk * 2 * kTileM + tile * kTileM + lane_group * 32 + lane] = best_idx;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_abort) *a.error_flag = s_abort;   // which wait gave up (see mbar_wait call sites)
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kWideTmemCols));
   }
 }
 
@@ -640,6 +882,7 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
   rc = make_row_map(&map_cent, cent, (int64_t)Z * C, DT);
   if (rc != RI_OK) return rc;
   RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAssignSmem));
+  RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem));
 
   for (int it = 0; it < p->n_iters; ++it) {
     const bool last = it == p->n_iters - 1;
@@ -652,9 +895,23 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
     aa.group_stride = N;
     aa.idesc = (1u << 4) | ((DT == RI_BF16 ? 1u : 0u) << 7) | ((DT == RI_BF16 ? 1u : 0u) << 10) |
                ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-    dim3 agrid((n_tok + kTileM - 1) / kTileM, problems);
-    kmeans_assign_kernel<<<agrid, kAssignThreads, kAssignSmem, s>>>(map_keys, map_cent, aa);
-    RI_LAUNCH_OK("kmeans_assign_kernel");
+    static const bool narrow = getenv("RI_KMEANS_NARROW") != nullptr;   // the 128-token form (A/B timing)
+    if (narrow) {
+      dim3 agrid((n_tok + kTileM - 1) / kTileM, problems);
+      kmeans_assign_kernel<<<agrid, kAssignThreads, kAssignSmem, s>>>(map_keys, map_cent, aa);
+      RI_LAUNCH_OK("kmeans_assign_kernel");
+    } else {
+      // blocks per CTA: enough CTAs for about a dozen waves over the SMs, at most 16 blocks each
+      WideArgs wa;
+      wa.a = aa;
+      const int n_blocks = (n_tok + 2 * kTileM - 1) / (2 * kTileM);
+      int per = (int)(((int64_t)n_blocks * problems) / (148 * 12));
+      per = per < 1 ? 1 : (per > 16 ? 16 : per);
+      wa.blocks_per_cta = per;
+      dim3 wgrid((n_blocks + per - 1) / per, problems);
+      kmeans_assign_wide_kernel<<<wgrid, kWideThreads, kWideSmem, s>>>(map_keys, map_cent, wa);
+      RI_LAUNCH_OK("kmeans_assign_wide_kernel");
+    }
     if ((rc0 = trace_stage("assign", s)) != RI_OK) return rc0;
 
     BucketArgs ba;
