@@ -510,6 +510,15 @@ def run_kmeans(geo, args, log):
         results[label] = {"segments": segs, "ms": round(ms, 3), "tflops": round(flop / ms / 1e9, 1), "flop": flop}
         log(f"{label}: {ms:.2f} ms, {flop / ms / 1e9:.1f} TFLOP/s")
     _, peak_tf, kind = measured_peaks()
+    # builds run back to back for tens of milliseconds: the sustained matmul figure is the denominator
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    sustained = None
+    if os.path.exists(path):
+        with open(path) as f:
+            sustained = json.load(f).get("bf16_tflops_sustained")
+    burst_tf = peak_tf
+    if sustained:
+        peak_tf, kind = float(sustained), kind + " (sustained)"
     main = results["reference schedule"]
     print(json.dumps({
         "metric": "prefill k-means clustering time (config 2)", "value": main["ms"], "unit": "ms", "n_gpus": 1,
@@ -519,8 +528,11 @@ def run_kmeans(geo, args, log):
                                f"{args.kmeans_iters} iterations, centring + value sums + cluster-contiguous layout",
                    "l2": "inputs larger than L2 (1.07 GB of keys)"},
         "roofline": {"bound": "tensor", "achieved": main["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
-                     "frac": round(main["tflops"] / peak_tf, 4), "peak_kind": "of " + kind, "traffic": None,
-                     "schedules": results},
+                     "frac": round(main["tflops"] / peak_tf, 4), "peak_kind": "of " + kind,
+                     "frac_of_burst_peak": round(main["tflops"] / burst_tf, 4),
+                     "note": "whole build (centring, assignment, bucket, update, layout) over the assignment GEMM's flops; "
+                             "the assignment kernel alone keeps the tensor pipe 67 % active (profiles/)",
+                     "traffic": None, "schedules": results},
     }), flush=True)
 
 
