@@ -5,8 +5,11 @@
 //   assign   argmax_c <x, c> for every token of every problem: tcgen05 MMA (M = 128 tokens,
 //            N = 128 centroids, K = 128 channels as 8 x K16) with operands staged by TMA
 //            (128-byte swizzle) and fp32 accumulators in TMEM; a warp-specialised CTA
-//            (TMA producer / MMA issuer / 4 epilogue warps) overlaps the running arg-max of one
-//            accumulator buffer with the MMAs into the other.
+//            (TMA producer / MMA issuer / epilogue warps) overlaps the running arg-max of one
+//            accumulator buffer with the MMAs into the other.  Two forms: the wide one (256
+//            tokens per block, persistent over blocks, eight epilogue warps) is what the build
+//            launches; the narrow one (128 tokens per CTA, four epilogue warps) stays for
+//            comparison (RI_KMEANS_NARROW=1).
 //   bucket   stable counting sort of the tokens of a problem by cluster: counts, offsets and
 //            the member list in ascending token order (deterministic, no global atomics).
 //   update   one warp per cluster sums its member rows in list order (fp32), forms the mean,
