@@ -210,6 +210,27 @@ int ri_kmeans_build(const ri_kmeans* p, void* stream);
  * pointers and the stream made explicit.  Index arrays, and key_data2/value_data2 of the concat,
  * may be pinned host memory (read through UVA), as in cache_hub/retroinfer_cache.py:124-173, :264-274.
  * ------------------------------------------------------------------------------------------ */
+/* batch_gemm_softmax.cu:171-198 (bound at :201-208) — D[b] = alpha * A[b] . B[b]^T rounded to the 16-bit type,
+ * softmax[b] = row-wise softmax of D[b], rounded.  A [batch, m, 128] with m <= 8 (the GQA group), B [batch, n, 128]
+ * with n a multiple of 8, D and softmax [batch, m, n]; norm and sum are scratch of batch * m * ceil(n / 256) floats
+ * each (per-block maxima and sums, as in the reference, where callers never read them); k must be 128, beta 0.
+ * The decode path itself does not use this operator: its kernel fuses the scores with the selection. */
+int ri_batch_gemm_softmax(const void* A, const void* B, void* D, float* norm, float* sum, void* softmax,
+                          int32_t batch_count, int32_t m, int32_t n, int32_t k, float alpha, float beta,
+                          int32_t dtype, void* stream);
+
+/* weighted_flash_decoding as an operator (the reference imports it from an external package; its call sites are
+ * cache_hub/retroinfer_cache.py:611-617 and :666-674).  Per group g and query head h, over the first d_seqlens[g]
+ * rows j of d_k/d_v [G, rows_stride, 128]:  s_j = q_h.k_j / sqrt(128),  w_j = d_weights[g, j] (1 when NULL),
+ *   out = sum_j e^{s_j} v_j / sum_j w_j e^{s_j},   lse = log sum_j w_j e^{s_j};
+ * when d_previous_out [G, gs, 128] and d_previous_lse [G, gs] are given, the result is merged with that partial
+ * result by log-sum-exp.  d_lse_out [G, gs] (natural log) may be NULL.  The decode path does not use this entry
+ * point (its kernel attends clusters in place); it serves callers of the operator. */
+int ri_weighted_flash_decoding(const void* d_q, const void* d_k, const void* d_v, const void* d_weights,
+                               const int32_t* d_seqlens, const void* d_previous_out, const float* d_previous_lse,
+                               void* d_out, float* d_lse_out, int32_t groups, int32_t group_size, int64_t rows_stride,
+                               int32_t dtype, void* stream);
+
 /* gather_copy.cu:25-96 — rows data_offsets[g, copy_start : copy_start+copy_num] of keys, values and
  * the per-row 16-bit metadata go to the first copy_num rows of the buffers. */
 int ri_gather_copy_vectors(const void* key_data, void* key_buffer, const void* value_data, void* value_buffer,

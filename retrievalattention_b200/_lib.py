@@ -103,6 +103,10 @@ def _load() -> C.CDLL:
     lib.ri_wb_sync.argtypes = [C.c_void_p]
     lib.ri_wb_rows_used.restype = C.c_int64
     lib.ri_wb_rows_used.argtypes = [C.c_void_p, C.c_int32]
+    lib.ri_batch_gemm_softmax.restype = C.c_int
+    lib.ri_batch_gemm_softmax.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_float, C.c_float, C.c_int32, C.c_void_p]
+    lib.ri_weighted_flash_decoding.restype = C.c_int
+    lib.ri_weighted_flash_decoding.argtypes = [C.c_void_p] * 9 + [C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_void_p]
     lib.ri_gather_copy_vectors.restype = C.c_int
     lib.ri_gather_copy_vectors.argtypes = [C.c_void_p] * 7 + [C.c_int32] * 6 + [C.c_void_p]
     lib.ri_gather_copy_and_concat.restype = C.c_int

@@ -39,7 +39,38 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBu
   return RI_OK;
 }
 
+template <int DT>
+int launch_operator(const AttendArgs& a, cudaStream_t s) {
+  const int clusters = min(a.G, max(1, attend_ctas() / kAttendCluster));
+  RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
+  RI_CUDA_OK(ri_launch_pdl_id(2, wave_attend_kernel<DT>, dim3(clusters * kAttendCluster), dim3(128), (size_t)kRingBytes, s, a));
+  return RI_OK;
+}
+
 }  // namespace
+
+// weighted_flash_decoding as an operator (call sites: cache_hub/retroinfer_cache.py:611-617, :666-674): dense
+// keys/values with a valid length per group, optional weights in the softmax denominator, optional merge with
+// a previous partial result, optional log-sum-exp output.  Runs the attend kernel over exact rows only.
+int launch_weighted_decoding(const void* q, const void* k, const void* v, const void* weights, const int32_t* seqlens,
+                             const void* prev_out, const float* prev_lse, void* out, float* lse_out, int groups,
+                             int group_size, int64_t stride, int dtype, cudaStream_t s) {
+  AttendArgs a = {};
+  a.q = static_cast<const uint4*>(q);
+  a.keys = static_cast<const uint4*>(k);
+  a.values = static_cast<const uint4*>(v);
+  a.n_exact = seqlens;
+  a.out = out;
+  a.N = stride;
+  a.G = groups; a.gs = group_size;
+  a.scale2 = RI_LOG2E * 0.08838834764831845f;
+  a.cost_est = RI_COST_EST; a.cost_exact = RI_COST_EXACT;
+  a.row_w = static_cast<const uint16_t*>(weights);
+  a.prev_out = static_cast<const uint16_t*>(prev_out);
+  a.prev_lse = prev_lse;
+  a.lse_out = lse_out;
+  return dtype == RI_BF16 ? launch_operator<RI_BF16>(a, s) : launch_operator<RI_F16>(a, s);
+}
 
 int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb) {
   return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s, eb) : launch<RI_F16>(p, L, s, eb);

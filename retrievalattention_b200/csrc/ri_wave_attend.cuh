@@ -71,6 +71,12 @@ struct AttendArgs {
   int cost_est, cost_exact;   // relative cost of an estimation / exact step when the steps are shared out
   uint16_t* const* copies;    // device array of n_copies more destinations of the output (other GPUs' gather buffers)
   int n_copies;
+  // operator form (ri_weighted_flash_decoding), all optional: a weight per exact row in the softmax denominator,
+  // a previous partial result to merge with, and the log-sum-exp of the result
+  const uint16_t* row_w;      // [G, N] in the 16-bit type
+  const uint16_t* prev_out;   // [G, gs, 128]
+  const float* prev_lse;      // [G, gs] natural log
+  float* lse_out;             // [G, gs] natural log
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -271,6 +277,17 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
   int stage = 0;
 #pragma unroll 1
   for (int s = lo; s < hi; ++s) {
+    float rw[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+    if (!LOCAL && a.row_w != nullptr && s >= es) {   // operator form: weights of this lane's four exact rows
+      const int b0 = (x_first + s - es) * 16 + 2 * t;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int row = min(b0 + jj * 8 + e, te - 1);
+          rw[jj][e] = Elem<DT>::from_bits(a.row_w[(int64_t)g * a.N + row]);
+        }
+    }
     cp_async_wait<kStages - 1>();           // the group of step s has landed (lane-private slots: no barrier)
     if (s == lo) RI_FT(10);
     const uint8_t* src = my_ring_ptr + stage * kStageStride;
@@ -311,6 +328,8 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
         }
         s2[jj][0] = (c[0] + c2[0]) * a.scale2;
         s2[jj][1] = (c[1] + c2[1]) * a.scale2;
+        w[jj][0] = rw[jj][0];
+        w[jj][1] = rw[jj][1];
       }
     }
 #pragma unroll
@@ -416,8 +435,20 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
       L += lc[c] * f;
       O += oc[c] * f;
     }
-    const uint16_t bits = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
     const int64_t idx = ((int64_t)g * gs + h) * RI_HEAD_DIM + ch;
+    float Mt = Ms;                         // log2-domain reference of L and O
+    if (a.prev_lse != nullptr) {           // operator form: merge with a previous partial result
+      const float mp = a.prev_lse[(int64_t)g * gs + h] * RI_LOG2E;
+      const float op = Elem<DT>::from_bits(a.prev_out[idx]);
+      const float Mn = fmaxf(M, mp);
+      Mt = Mn == -INFINITY ? 0.f : Mn;
+      const float fa = M == -INFINITY ? 0.f : exp2f(M - Mt), fb = mp == -INFINITY ? 0.f : exp2f(mp - Mt);
+      L = L * fa + fb;
+      O = O * fa + op * fb;
+    }
+    if (a.lse_out != nullptr && ch == 0)
+      a.lse_out[(int64_t)g * gs + h] = L > 0.f ? (Mt + log2f(L)) * 0.6931471805599453f : -INFINITY;
+    const uint16_t bits = Elem<DT>::bits(L > 0.f ? O / L : 0.f);
     reinterpret_cast<uint16_t*>(a.out)[idx] = bits;
     for (int c = 0; c < a.n_copies; ++c) a.copies[c][idx] = bits;   // several GPUs: the other ranks' gather buffers
   }
@@ -446,6 +477,7 @@ inline void fill_attend_args(const ri_wave_layer& p, const Layout& L, const Exec
   a.scale2 = RI_LOG2E * 0.08838834764831845f;
   a.copies = nullptr;
   a.n_copies = 0;
+  a.row_w = nullptr; a.prev_out = nullptr; a.prev_lse = nullptr; a.lse_out = nullptr;
   static const int cost_est = getenv("RI_COST_EST") ? atoi(getenv("RI_COST_EST")) : RI_COST_EST;
   static const int cost_exact = getenv("RI_COST_EXACT") ? atoi(getenv("RI_COST_EXACT")) : RI_COST_EXACT;
   a.cost_est = cost_est > 0 ? cost_est : 1;

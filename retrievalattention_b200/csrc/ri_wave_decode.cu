@@ -142,6 +142,20 @@ extern "C" int ri_wave_gather_wait(const ri_wave_gather* g, void* stream) {
   return launch_gather_wait(*g, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int ri_weighted_flash_decoding(const void* d_q, const void* d_k, const void* d_v, const void* d_weights,
+                                          const int32_t* d_seqlens, const void* d_previous_out,
+                                          const float* d_previous_lse, void* d_out, float* d_lse_out, int32_t groups,
+                                          int32_t group_size, int64_t rows_stride, int32_t dtype, void* stream) {
+  RI_REQUIRE(d_q && d_k && d_v && d_seqlens && d_out, "ri_weighted_flash_decoding: null pointer");
+  RI_REQUIRE((d_previous_out == nullptr) == (d_previous_lse == nullptr), "previous_out and previous_lse go together");
+  RI_REQUIRE(groups >= 1 && groups <= 65535 && group_size >= 1 && group_size <= kMaxHeads && rows_stride >= 1,
+             "ri_weighted_flash_decoding: bad sizes");
+  RI_REQUIRE(dtype == RI_BF16 || dtype == RI_F16, "dtype=%d unsupported", dtype);
+  RI_REQUIRE(((uintptr_t)d_q | (uintptr_t)d_k | (uintptr_t)d_v) % 16 == 0, "q, k and v must be 16-byte aligned");
+  return launch_weighted_decoding(d_q, d_k, d_v, d_weights, d_seqlens, d_previous_out, d_previous_lse, d_out, d_lse_out,
+                                  groups, group_size, rows_stride, dtype, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ri_steady_append(const void* d_k, const void* d_v, void* d_steady_keys, void* d_steady_values,
                                 const int32_t* d_position, int32_t groups, int32_t steady_stride, void* stream) {
   RI_REQUIRE(d_k && d_v && d_steady_keys && d_steady_values && d_position, "ri_steady_append: null pointer");

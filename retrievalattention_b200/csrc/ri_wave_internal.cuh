@@ -65,6 +65,9 @@ int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 // `eb` (optional): attend over a dense execution buffer instead of the cluster-contiguous store.
 struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
 int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr);
+int launch_weighted_decoding(const void* q, const void* k, const void* v, const void* weights, const int32_t* seqlens,
+                             const void* prev_out, const float* prev_lse, void* out, float* lse_out, int groups,
+                             int group_size, int64_t stride, int dtype, cudaStream_t s);
 // scan + select + attend as one kernel (one 8-CTA cluster per group).
 int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather = nullptr);
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s);

@@ -88,6 +88,58 @@ def _p(t: torch.Tensor) -> int:
     return t.data_ptr()
 
 
+def batch_gemm_softmax(A, B, D, Norm, Sum, Softmax, batch_count, m, n, k, alpha=1.0, beta=0.0):
+    """``retroinfer_kernels.batch_gemm_softmax`` (src/batch_gemm_softmax.cu:201-208): ``D = alpha * A @ B^T`` and
+    ``Softmax = softmax(D, -1)``, both in the dtype of ``A``; ``Norm``/``Sum`` are float32 scratch of
+    ``batch_count * m * ceil(n / 256)`` elements.  On the current stream."""
+    for t in (A, B, D, Norm, Sum, Softmax):
+        if not (t.is_cuda and t.is_contiguous()):
+            raise ValueError("batch_gemm_softmax: tensors must be contiguous CUDA tensors")
+    if B.dtype != A.dtype or D.dtype != A.dtype or Softmax.dtype != A.dtype:
+        raise TypeError("batch_gemm_softmax: A, B, D and Softmax must share one dtype")
+    if Norm.dtype != torch.float32 or Sum.dtype != torch.float32:
+        raise TypeError("batch_gemm_softmax: Norm and Sum must be float32")
+    blocks = (n + 255) // 256
+    if A.numel() != batch_count * m * k or B.numel() != batch_count * n * k or D.numel() != batch_count * m * n or \
+            Softmax.numel() != D.numel() or Norm.numel() < batch_count * m * blocks or Sum.numel() < batch_count * m * blocks:
+        raise ValueError("batch_gemm_softmax: tensor sizes do not match batch_count, m, n, k")
+    _lib.check(_lib.lib.ri_batch_gemm_softmax(_p(A), _p(B), _p(D), _p(Norm), _p(Sum), _p(Softmax), batch_count, m, n, k,
+                                              float(alpha), float(beta), _lib.dtype_code(A.dtype), _lib.current_stream()),
+               "ri_batch_gemm_softmax")
+
+
+def weighted_flash_decoding(q, k, v, weights=None, *, previous_out=None, previous_lse=None, cache_seqlens=None,
+                            return_softmax_lse=False):
+    """The operator the reference imports as ``weighted_flash_decoding`` (call sites
+    cache_hub/retroinfer_cache.py:611-617, :666-674).  ``q`` [G, 1, gs, 128]; ``k``/``v`` [G, L, 1, 128];
+    ``weights`` [G, 1, 1, L] (softmax-denominator weight of every row) or None; ``cache_seqlens`` [G] int32 or None
+    (all L rows); ``previous_out`` [G, 1, gs, 128] with ``previous_lse`` [G, gs, 1] (float32, natural log): a partial
+    result to merge with.  Returns ``out`` [G, 1, gs, 128], and ``lse`` [G, gs, 1] when asked."""
+    g, one, gs, d = q.shape
+    length = k.shape[1]
+    if one != 1 or d != 128 or k.shape != (g, length, 1, d) or v.shape != k.shape:
+        raise ValueError("weighted_flash_decoding: expected q [G,1,gs,128] and k, v [G,L,1,128]")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if cache_seqlens is None:
+        cache_seqlens = torch.full((g,), length, dtype=torch.int32, device=q.device)
+    cache_seqlens = cache_seqlens.to(torch.int32).contiguous()
+    if weights is not None:
+        weights = weights.to(q.dtype).reshape(g, length).contiguous()
+    if (previous_out is None) != (previous_lse is None):
+        raise ValueError("weighted_flash_decoding: previous_out and previous_lse go together")
+    if previous_out is not None:
+        previous_out = previous_out.to(q.dtype).reshape(g, gs, d).contiguous()
+        previous_lse = previous_lse.to(torch.float32).reshape(g, gs).contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty((g, gs, 1), dtype=torch.float32, device=q.device) if return_softmax_lse else None
+    _lib.check(_lib.lib.ri_weighted_flash_decoding(
+        _p(q), _p(k), _p(v), None if weights is None else _p(weights), _p(cache_seqlens),
+        None if previous_out is None else _p(previous_out), None if previous_lse is None else _p(previous_lse),
+        _p(out), None if lse is None else _p(lse), g, gs, length, _lib.dtype_code(q.dtype), _lib.current_stream()),
+        "ri_weighted_flash_decoding")
+    return (out, lse) if return_softmax_lse else out
+
+
 def gather_copy_vectors(key_data, key_buffer, value_data, value_buffer, src_metadata, dst_metadata, data_offsets,
                         groups, data_length, buffer_length, index_size, copy_start, copy_num):
     """gather_copy.cu:25-96 (same argument list)."""
