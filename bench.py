@@ -119,7 +119,8 @@ class Workload:
 
     def step_body(self):
         """One decode step of the hot path over all layers on the current stream: per layer the
-        reference's two calls (model_hub/LLM.py:116-117): the steady append and the decode kernel.
+        reference's two calls (model_hub/LLM.py:116-117), which end up as one launch: the decode kernel
+        stores the step's key/value rows into the steady zone before it attends.
         Several GPUs: the head slices of all ranks -> [B, 1, Hq, d] for the output projection, either
         written by the decode kernel into every rank's buffer (then one bounded flag wait per layer) or
         by an NCCL all-gather."""
@@ -155,10 +156,10 @@ class Workload:
             self.step_body()
 
     def launches_per_step(self):
-        # per layer: steady append, then the single decode kernel (RI_WAVE_STAGED=1: scan, select, attend),
-        # plus the flag wait of the peer-store gather
+        # per layer: the single decode kernel, which also appends the step's key/value rows (RI_WAVE_STAGED=1:
+        # steady append, scan, select, attend), plus the flag wait of the peer-store gather
         staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")
-        return ((4 if staged else 2) + (1 if self.peer is not None else 0)) * self.geo.layers
+        return ((4 if staged else 1) + (1 if self.peer is not None else 0)) * self.geo.layers
 
     def static_len(self):
         return int(self.cache._per_device[str(self.device)]["static_len"].item())

@@ -79,6 +79,11 @@ typedef struct ri_wave_layer {
   int64_t* d_retrieved_ids;      /* [G, P] ranked cluster ids (reference: cluster_ids, :575) */
   int32_t* d_retrieved_kept;     /* [G] how many of them fit the page budget */
   int64_t* d_estimated_ids;      /* [G, E] */
+  /* optional (may be NULL, both or neither): this step's key/value rows [G, 128].  When given, the decode entry
+   * points store them into the steady zone at row *d_static_len - 1 before attending, which saves the separate
+   * ri_steady_append launch (decode_update_kv_cache + compute of the reference in one launch). */
+  const void* d_new_keys;
+  const void* d_new_values;
 } ri_wave_layer;
 
 /* Bytes of scratch one ri_wave_decode_layer call needs for this geometry (no device work). */

@@ -29,6 +29,7 @@ class WaveLayer(C.Structure):
         ("d_steady_keys", C.c_void_p), ("d_steady_values", C.c_void_p), ("d_static_len", C.c_void_p),
         ("d_q", C.c_void_p), ("d_out", C.c_void_p), ("d_scratch", C.c_void_p),
         ("d_retrieved_ids", C.c_void_p), ("d_retrieved_kept", C.c_void_p), ("d_estimated_ids", C.c_void_p),
+        ("d_new_keys", C.c_void_p), ("d_new_values", C.c_void_p),
     ]
 
 

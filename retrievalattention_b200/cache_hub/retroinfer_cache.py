@@ -41,12 +41,17 @@ class retroinfer_cache(KV_Cache):
                  static_pattern_start: int, static_pattern_end: int, core: int, n_centroids: int, n_segment: int,
                  nprobe: int, max_compute_cluster_num: int, cache_unit_size: int, cache_cluster_num: int,
                  num_gpus: int, model_size: int, use_cluster_estimation: bool = False,
-                 kv_on_host: bool = False) -> None:
+                 kv_on_host: bool = False, fuse_append: bool = True) -> None:
         super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
                          layer_mapping, num_gpus, model_size)
         if head_dim != 128:
             raise ValueError("the wave-index kernels are built for head_dim 128 (as the reference's copy kernels are)")
         self.valid_start = valid_start
+        # fuse_append (not in the reference): decode_update_kv_cache only hands the new rows to the layer and the
+        # decode kernel of the following compute() stores them into the steady zone itself (one launch less per
+        # layer).  The two calls always come in pairs (attn_hub.retroinfer_decode_attn); the rows passed must stay
+        # unchanged until that compute().  HBM tier only.
+        self.fuse_append = bool(fuse_append) and not kv_on_host
         self.static_pattern_start = static_pattern_start
         self.static_pattern_end = static_pattern_end
         self.static_pattern_total = static_pattern_start + static_pattern_end
@@ -224,10 +229,13 @@ class retroinfer_cache(KV_Cache):
                 "re-indexing after 1024 generated tokens (reference _update_kv_cache, :462-524) is not built yet")
         per = self._per_device[self.layer_mapping[str(layer_idx)]]
         g = self.batch_groups
-        wave.steady_append(key_states.contiguous(), value_states.contiguous(),
-                           self.steady_zone_keys[layer_idx].view(g, self.static_stride, self.head_dim),
-                           self.steady_zone_values[layer_idx].view(g, self.static_stride, self.head_dim),
-                           per["append_pos"])
+        if self.fuse_append:
+            self._layers[layer_idx].append_with_next_compute(key_states.contiguous(), value_states.contiguous())
+        else:
+            wave.steady_append(key_states.contiguous(), value_states.contiguous(),
+                               self.steady_zone_keys[layer_idx].view(g, self.static_stride, self.head_dim),
+                               self.steady_zone_values[layer_idx].view(g, self.static_stride, self.head_dim),
+                               per["append_pos"])
         if layer_idx == self.layer_num - 1:
             self.context += 1
             self.static_pattern_total += 1

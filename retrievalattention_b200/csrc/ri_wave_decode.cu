@@ -36,16 +36,18 @@ int validate(const ri_wave_layer* p) {
               (uintptr_t)p->d_steady_keys | (uintptr_t)p->d_steady_values | (uintptr_t)p->d_q) % 16 == 0,
              "tensor pointers must be 16-byte aligned");
   RI_REQUIRE((uintptr_t)p->d_scratch % 128 == 0, "the scratch must be 128-byte aligned");
+  RI_REQUIRE((p->d_new_keys == nullptr) == (p->d_new_values == nullptr), "d_new_keys and d_new_values go together");
+  RI_REQUIRE(((uintptr_t)p->d_new_keys | (uintptr_t)p->d_new_values) % 16 == 0, "new key/value rows must be 16-byte aligned");
   return RI_OK;
 }
 
 __global__ void steady_append_kernel(const uint4* __restrict__ k, const uint4* __restrict__ v, uint4* sk, uint4* sv,
-                                     const int32_t* __restrict__ pos, int groups, int stride) {
+                                     const int32_t* __restrict__ pos, int pos_offset, int groups, int stride) {
   ri_pdl_enter();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece each
   if (i >= groups * 16) return;
   const int g = i >> 4, c = i & 15;
-  const int p = *pos;
+  const int p = *pos + pos_offset;
   if (p < 0 || p >= stride) return;
   sk[((int64_t)g * stride + p) * 16 + c] = k[i];
   sv[((int64_t)g * stride + p) * 16 + c] = v[i];
@@ -111,6 +113,14 @@ extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
   // RI_WAVE_STAGED=1 keeps the three-kernel form (profiling one stage at a time, A/B timing)
   static const bool staged = getenv("RI_WAVE_STAGED") && atoi(getenv("RI_WAVE_STAGED")) != 0;
   if (!staged && fused_supported(*p)) return launch_fused(*p, L, s);
+  if (p->d_new_keys) {   // the three-kernel form appends with the stand-alone kernel (row *d_static_len - 1)
+    const int n = p->groups * 16;
+    RI_CUDA_OK(ri_launch_pdl_id(4, steady_append_kernel, dim3((n + 255) / 256), dim3(256), 0, s,
+                                static_cast<const uint4*>(p->d_new_keys), static_cast<const uint4*>(p->d_new_values),
+                                static_cast<uint4*>(const_cast<void*>(p->d_steady_keys)),
+                                static_cast<uint4*>(const_cast<void*>(p->d_steady_values)), p->d_static_len, -1, p->groups,
+                                p->steady_stride));
+  }
   if ((rc = launch_scan(*p, L, s)) != RI_OK) return rc;
   if ((rc = launch_select(*p, L, s)) != RI_OK) return rc;
   return launch_attend(*p, L, s);
@@ -163,7 +173,7 @@ extern "C" int ri_steady_append(const void* d_k, const void* d_v, void* d_steady
   const int n = groups * 16;
   RI_CUDA_OK(ri_launch_pdl_id(4, steady_append_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream),
                            static_cast<const uint4*>(d_k), static_cast<const uint4*>(d_v),
-                           static_cast<uint4*>(d_steady_keys), static_cast<uint4*>(d_steady_values), d_position, groups,
+                           static_cast<uint4*>(d_steady_keys), static_cast<uint4*>(d_steady_values), d_position, 0, groups,
                            steady_stride));
   return RI_OK;
 }

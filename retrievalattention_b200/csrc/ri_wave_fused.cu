@@ -36,6 +36,11 @@ struct FusedArgs {
   uint32_t* const* flag_slots;
   const uint32_t* epoch;
   int n_ranks;
+  // this step's key/value rows [G, 128] to append to the steady zone (row static_len - 1) first; null: already there
+  const uint4* new_k;
+  const uint4* new_v;
+  uint4* steady_k_w;
+  uint4* steady_v_w;
   int persist_off;   // byte offset, behind the ring and the scores, of the lists that outlive the selection
   int cap;           // estimation entries a CTA can keep in shared memory (multiple of 16)
 };
@@ -583,6 +588,13 @@ wave_fused_kernel(FusedArgs f) {
   int static_len;     // fetched now (not where the compiler would sink the load to: the middle of phase 2)
   asm volatile("ld.global.b32 %0, [%1];" : "=r"(static_len) : "l"(f.att.static_len));
 
+  // the new token's rows go into the steady zone now; the attend phase reads them several cluster barriers later
+  if (f.new_k != nullptr && rank == 0 && tid < 32 && static_len >= 1 && static_len <= f.att.steady_stride) {
+    const int64_t dst = ((int64_t)g * f.att.steady_stride + static_len - 1) * 16 + (tid & 15);
+    if (tid < 16) f.steady_k_w[dst] = f.new_k[(int64_t)g * 16 + tid];
+    else f.steady_v_w[dst] = f.new_v[(int64_t)g * 16 + (tid & 15)];
+  }
+
   // ---- phase 1: scores of this CTA's slice ----
   RI_FT(0);
   scan_slice<DT>(f, g, lo, hi, ring, s_sc, part_m, part_s);
@@ -680,6 +692,10 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wav
   f.alpha = 0.08838834764831845f;
   f.views = p.d_retrieved_ids != nullptr;
   f.flag_slots = nullptr; f.epoch = nullptr; f.n_ranks = 0;
+  f.new_k = static_cast<const uint4*>(p.d_new_keys);
+  f.new_v = static_cast<const uint4*>(p.d_new_values);
+  f.steady_k_w = static_cast<uint4*>(const_cast<void*>(p.d_steady_keys));
+  f.steady_v_w = static_cast<uint4*>(const_cast<void*>(p.d_steady_values));
   if (gather) {
     f.att.copies = reinterpret_cast<uint16_t* const*>(gather->d_out_slots);
     f.att.n_copies = gather->n_ranks;

@@ -84,6 +84,7 @@ class WaveIndexLayer:
                       scratch=scratch)
         for k, v in self.t.items():
             assert v.is_cuda and v.is_contiguous(), k
+        self.pending_kv = None
         self.retrieved_ids = self.retrieved_kept = self.estimated_ids = None
         if want_ids:
             self.retrieved_ids = torch.zeros((g, shape.nprobe), dtype=torch.int64, device=dev)
@@ -108,6 +109,20 @@ class WaveIndexLayer:
         assert q.is_cuda and q.is_contiguous() and q.dtype == s.dtype and q.numel() == s.groups * s.group_size * 128
         assert out.is_cuda and out.is_contiguous() and out.dtype == s.dtype and out.numel() == q.numel()
         self.params.d_q, self.params.d_out = q.data_ptr(), out.data_ptr()
+        kv, self.pending_kv = self.pending_kv, None
+        if kv is None:
+            self.params.d_new_keys = self.params.d_new_values = None
+        else:                      # this step's rows: the decode call appends them itself (one launch less)
+            self.params.d_new_keys, self.params.d_new_values = kv[0].data_ptr(), kv[1].data_ptr()
+            self._kv_alive = kv    # until the next call
+
+    def append_with_next_compute(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Hand this step's key/value rows ``[G, 128]`` (any shape with that many elements) to the next
+        ``compute`` call, which stores them at row ``static_len - 1`` of the steady zone before attending."""
+        s = self.shape
+        assert k.is_cuda and k.is_contiguous() and k.dtype == s.dtype and k.numel() == s.groups * 128
+        assert v.is_cuda and v.is_contiguous() and v.dtype == s.dtype and v.numel() == k.numel()
+        self.pending_kv = (k, v)
 
     def compute(self, q: torch.Tensor, out: torch.Tensor | None = None, gather=None) -> torch.Tensor:
         """scan + select + attend (one kernel) on the current stream.  ``q``: [B, 1, Hq, 128] (or [G, gs, 128]).

@@ -185,6 +185,32 @@ def test_steady_append_and_growing_static_len():
     assert torch.equal(layer.t["steady_keys"].cpu(), cpu["steady_keys"])
 
 
+@pytest.mark.parametrize("want_ids", [False, True])
+def test_append_done_by_the_decode_kernel(want_ids):
+    """The step's key/value rows handed to the decode call: the kernel stores them at row static_len - 1 of the
+    steady zone before it attends — same steady zone and same output as a separate append followed by compute."""
+    case = CASES["small_gs4"]
+    cpu = build_cpu_index(case)
+    layer = to_gpu_layer(case, cpu, SINK + RECENT, want_ids=want_ids)
+    pos = layer.t["static_len"]
+    q = queries(case, seed=9)
+    for step in range(3):
+        k_new = torch.randn((case.batch, 1, case.kv_heads, 128)).to(case.dtype)
+        v_new = torch.randn((case.batch, 1, case.kv_heads, 128)).to(case.dtype)
+        cpu["steady_keys"][:, SINK + RECENT + step] = k_new.reshape(case.groups, 128)
+        cpu["steady_values"][:, SINK + RECENT + step] = v_new.reshape(case.groups, 128)
+        pos += 1                                   # the step attends static_len rows, the new one included
+        layer.append_with_next_compute(k_new.cuda(), v_new.cuda())
+        out = layer.compute(q.cuda())
+        ref_out, _ = run_oracle(case, cpu, q, SINK + RECENT + step + 1)
+        err = (out.cpu().float() - ref_out.float()).abs()
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3
+        again = layer.compute(q.cuda())            # no rows pending: nothing is appended, same result
+        assert torch.equal(out.view(torch.int16), again.view(torch.int16))
+    assert torch.equal(layer.t["steady_keys"].cpu(), cpu["steady_keys"])
+    assert torch.equal(layer.t["steady_values"].cpu(), cpu["steady_values"])
+
+
 def test_invalid_arguments_are_rejected():
     import ctypes as C
     from retrievalattention_b200 import _lib
