@@ -31,7 +31,7 @@ def module_path() -> str:
 def build(reference_root: str | None = None, force: bool = False) -> str | None:
     """Returns the path of the built module, or None when the reference checkout is
     not present (then a previously built module, if any, keeps being used)."""
-    reference_root = reference_root or os.environ.get("RI_REFERENCE_ROOT", "/root/reference")
+    reference_root = reference_root or os.environ.get("RI_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
     src = os.path.join(reference_root, SRC_REL)
     out = module_path()
     if not os.path.exists(src):

@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py <reference checkout>      (or RI_REFERENCE_ROOT in the environment)
 
 * ``kmeans_*.pt`` — outputs of the reference's own ``cache_hub/kmeans.py``
   (``segment_k_means``) executed unmodified on CPU tensors under the Triton
@@ -154,7 +154,7 @@ def make_wave_buffer():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RI_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
     which = sys.argv[2] if len(sys.argv) > 2 else "all"
     if which in ("all", "kmeans"):
         make_kmeans(root)
