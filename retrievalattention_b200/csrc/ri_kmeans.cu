@@ -710,7 +710,7 @@ __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
   if (a.size_dt) a.size_dt[(int64_t)problem * a.n_cen + c] = Elem<DT>::bits((float)cnt);
 
   float ks[4] = {0, 0, 0, 0}, vs[4] = {0, 0, 0, 0};
-  constexpr int kUnroll = 8;
+  constexpr int kUnroll = 4;
   for (int j0 = 0; j0 < cnt; j0 += kUnroll) {
     int rows[kUnroll];
     uint2 kv[kUnroll], vv[kUnroll], rk[kUnroll];
