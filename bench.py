@@ -107,7 +107,7 @@ class Workload:
                 try:
                     from retrievalattention_b200.head_shard import PeerGather
                     self.peer = PeerGather(self.shard, geo.layers, geo.batch, geo.q_heads, geo.head_dim, torch.bfloat16,
-                                           device, groups=geo.batch * geo.kv_heads, group=self.gather.group)
+                                           device, group=self.gather.group)
                 except Exception as exc:     # noqa: BLE001 — any set-up failure falls back to the collective
                     self.peer_error = repr(exc)[:200]
                     if log:
@@ -414,7 +414,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
                    "parallelism": (f"{world} ranks: {wl.shard.head_shards} KV-head shards x {wl.shard.batch_shards} batch "
                                    f"shards; per rank {lg.kv_heads} kv heads x batch {lg.batch} = {wl.shape.groups} groups; "
                                    + ("head slices stored into every rank's gather buffer by the decode kernel "
-                                      "(peer stores over NVLink), one bounded flag wait per layer"
+                                      "(peer stores over NVLink), one flag exchange with a bounded wait per layer"
                                       if wl.peer is not None else "one NCCL all-gather of the head slices per layer"))
                                   if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (each layer-step touches its own ~110 MB; ~3.5 GB per step)",

@@ -126,28 +126,31 @@ int ri_wave_attend_buffer(const ri_wave_layer* p, const void* d_exec_keys, const
  * exchange is the gather of the ranks' [G, gs, 128] output slices before the model's output
  * projection (the reference has no multi-GPU form of this path).  Instead of a collective after
  * the kernel, ri_wave_decode_layer_gather makes the decode kernel store every output value into the
- * gather buffer of EVERY rank of the group (peer-mapped addresses over NVLink); each CTA, once its
- * values are stored, writes the step's epoch into its own flag word on every rank (stores, CTA
- * barrier, one system-scope fence, flag: no tickets, nothing waits).  ri_wave_gather_wait enqueues
- * a small kernel that waits until all flag words of all ranks of this layer hold the epoch;
- * whatever is enqueued after it may read the complete gather buffer.  The wait is bounded: after
- * wait_limit_us it sets *d_error and returns, so a missing rank never hangs the GPU.
- * *d_epoch is read on the device by both calls: the caller increases it once per step (the same
- * value on every rank) before the step's first launch. */
+ * gather buffer of EVERY rank of the group (peer-mapped addresses over NVLink; plain stores, no
+ * fence inside the kernel — a system-scope fence in each of its CTAs cost 7 us per layer).
+ * ri_wave_gather_wait, enqueued behind it on the same stream, runs one small kernel that (1) writes
+ * the step's epoch into this rank's flag word on every rank — the decode kernel has completed by
+ * then, so its stores are ordered before the flags, and each flag store follows a system-scope fence
+ * — and (2) waits until the flag words of all ranks hold the epoch; whatever is enqueued after it
+ * may read the complete gather buffer.  The wait is bounded: after wait_limit_us it sets *d_error
+ * and returns, so a missing rank never hangs the GPU.
+ * *d_epoch is read on the device: the caller increases it once per step (the same value on every
+ * rank) before the step's first launch. */
 typedef struct ri_wave_gather {
   int32_t n_ranks;                 /* ranks of the gather group, 2..64 */
   int32_t rank;                    /* this rank's place in it */
-  int32_t n_flags;                 /* flag words per rank and layer = CTAs of the decode kernel = 8 * groups */
   int32_t wait_limit_us;           /* <= 0: one second */
+  int32_t reserved;
   void* const* d_out_slots;        /* device array [n_ranks]: where this rank's output slice goes on each rank */
-  uint32_t* const* d_flag_slots;   /* device array [n_ranks]: this rank's row of n_flags flag words (this layer) on each rank */
-  const uint32_t* d_flags;         /* local: this layer's flag words, [n_ranks][n_flags] */
+  uint32_t* const* d_flag_slots;   /* device array [n_ranks]: this rank's flag word (this layer) on each rank */
+  const uint32_t* d_flags;         /* local: this layer's flag words, one per rank */
   const uint32_t* d_epoch;         /* local: [1] the current step's epoch */
   int32_t* d_error;                /* local: set to 1 when a wait ran out */
 } ri_wave_gather;
-/* ri_wave_decode_layer plus the stores and the flags described above (p->d_out is written too).
+/* ri_wave_decode_layer plus the stores described above (p->d_out is written too).
  * RI_ERR_INVALID for geometries the single decode kernel does not cover (more than 8192 centroids). */
 int ri_wave_decode_layer_gather(const ri_wave_layer* p, const ri_wave_gather* g, void* stream);
+/* Raise this rank's flags, then wait (bounded) for every rank's. */
 int ri_wave_gather_wait(const ri_wave_gather* g, void* stream);
 
 /* Views into the scratch (device pointers valid after ri_wave_select), for tests. */

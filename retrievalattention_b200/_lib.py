@@ -37,7 +37,7 @@ class WaveGather(C.Structure):
     """Mirror of ``struct ri_wave_gather``."""
 
     _fields_ = [
-        ("n_ranks", C.c_int32), ("rank", C.c_int32), ("n_flags", C.c_int32), ("wait_limit_us", C.c_int32),
+        ("n_ranks", C.c_int32), ("rank", C.c_int32), ("wait_limit_us", C.c_int32), ("reserved", C.c_int32),
         ("d_out_slots", C.c_void_p), ("d_flag_slots", C.c_void_p), ("d_flags", C.c_void_p),
         ("d_epoch", C.c_void_p), ("d_error", C.c_void_p),
     ]

@@ -131,7 +131,6 @@ int validate_gather(const ri_wave_gather* g) {
   RI_REQUIRE(g != nullptr, "ri_wave_gather is null");
   RI_REQUIRE(g->n_ranks >= 2 && g->n_ranks <= 64, "n_ranks=%d unsupported (2..64)", g->n_ranks);
   RI_REQUIRE(g->rank >= 0 && g->rank < g->n_ranks, "rank=%d outside the group of %d", g->rank, g->n_ranks);
-  RI_REQUIRE(g->n_flags >= 1 && (int64_t)g->n_flags * g->n_ranks <= (1 << 22), "n_flags=%d out of range", g->n_flags);
   RI_REQUIRE(g->d_out_slots && g->d_flag_slots && g->d_flags && g->d_epoch && g->d_error, "ri_wave_gather: null pointer");
   return RI_OK;
 }

@@ -31,11 +31,6 @@ struct FusedArgs {
   float* scores;     // global copy of the scores (a view for tests), written only when `views`
   float alpha;
   int views;         // also fill the global lists and views (tests, callers that asked for the id outputs)
-  // several GPUs: this rank's row of flag words on every rank of its gather group (one word per CTA), raised
-  // once the CTA's outputs are stored there (att.copies); null when there is no gather
-  uint32_t* const* flag_slots;
-  const uint32_t* epoch;
-  int n_ranks;
   // this step's key/value rows [G, 128] to append to the steady zone (row static_len - 1) first; null: already there
   const uint4* new_k;
   const uint4* new_v;
@@ -623,39 +618,32 @@ wave_fused_kernel(FusedArgs f) {
   if (local) attend_group<DT, true>(f.att, g, rank, ring, &ll);
   else attend_group<DT, false>(f.att, g, rank, ring);
   RI_FT(13);
-
-  // ---- several GPUs: this CTA's outputs are stored on every rank (before the cluster barrier that ends the attend
-  //      phase): one system-scope fence, then the step's epoch into this CTA's flag word on every rank ----
-  if (f.flag_slots != nullptr && tid == 0) {
-    const uint32_t epoch = *f.epoch;
-    const int word = blockIdx.y * gridDim.x + blockIdx.x;
-    __threadfence_system();
-    for (int p = 0; p < f.n_ranks; ++p)
-      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f.flag_slots[p] + word), "r"(epoch) : "memory");
-  }
 }
 
-// Waits (bounded) until every flag word of every rank of this layer holds this step's epoch.
-__global__ void gather_wait_kernel(const uint32_t* flags, const uint32_t* epoch, int32_t* error, int n_words,
-                                   long long limit_ns) {
+// After the decode kernel of the same stream: raise this rank's flag on every rank, then wait (bounded) until
+// every rank's flag here holds this step's epoch.  Thread r looks after rank r.
+__global__ void gather_signal_wait_kernel(uint32_t* const* flag_slots, const uint32_t* flags, const uint32_t* epoch,
+                                          int32_t* error, int n_ranks, long long limit_ns) {
   ri_pdl_enter();
+  const int r = threadIdx.x;
+  if (r >= n_ranks) return;
   const uint32_t expected = *epoch;
+  // the decode kernel has completed (stream order), so its stores to the other GPUs happen before this fence,
+  // and the fence orders them before the flag at system scope
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag_slots[r]), "r"(expected) : "memory");
   unsigned long long t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  bool ok = true;
-  for (int i = threadIdx.x; i < n_words && ok; i += blockDim.x) {
-    long long spins = 0;
-    for (;;) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
-      if ((int32_t)(v - expected) >= 0) break;
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if ((long long)(now - t0) > limit_ns || ++spins > (1ll << 26)) { ok = false; break; }   // give up: time or count
-      __nanosleep(64);
-    }
+  long long spins = 0;
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+    if ((int32_t)(v - expected) >= 0) break;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if ((long long)(now - t0) > limit_ns || ++spins > (1ll << 26)) { *error = 1; break; }   // give up: time or count
+    __nanosleep(64);
   }
-  if (!ok) *error = 1;
 }
 
 // Shared memory one CTA may use when two of them share an SM, minus the kernel's static part.
@@ -691,7 +679,6 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wav
   f.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(p.d_scratch) + L.scores);
   f.alpha = 0.08838834764831845f;
   f.views = p.d_retrieved_ids != nullptr;
-  f.flag_slots = nullptr; f.epoch = nullptr; f.n_ranks = 0;
   f.new_k = static_cast<const uint4*>(p.d_new_keys);
   f.new_v = static_cast<const uint4*>(p.d_new_values);
   f.steady_k_w = static_cast<uint4*>(const_cast<void*>(p.d_steady_keys));
@@ -699,11 +686,7 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wav
   if (gather) {
     f.att.copies = reinterpret_cast<uint16_t* const*>(gather->d_out_slots);
     f.att.n_copies = gather->n_ranks;
-    f.flag_slots = gather->d_flag_slots;
-    f.epoch = gather->d_epoch;
-    f.n_ranks = gather->n_ranks;
-    RI_REQUIRE(gather->n_flags == kSelectCluster * p.groups, "n_flags=%d, the decode kernel has %d CTAs", gather->n_flags,
-               kSelectCluster * p.groups);
+
   }
   RI_REQUIRE(fused_supported(p), "the single-kernel path needs n_centroids <= %d", kMaxSlice * kSelectCluster);
   RI_REQUIRE((size_t)f.sel.p_pad * 44 <= (size_t)kScoreOffset, "nprobe=%d too large", p.nprobe);
@@ -743,9 +726,8 @@ int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const 
 
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s) {
   const long long limit_ns = (g.wait_limit_us > 0 ? (long long)g.wait_limit_us : 1000000ll) * 1000ll;
-  const int n_words = g.n_ranks * g.n_flags;
-  const int threads = n_words < 1024 ? ((n_words + 31) / 32) * 32 : 1024;
-  RI_CUDA_OK(ri_launch_pdl_id(6, gather_wait_kernel, dim3(1), dim3(threads), 0, s, g.d_flags, g.d_epoch, g.d_error, n_words, limit_ns));
+  RI_CUDA_OK(ri_launch_pdl_id(6, gather_signal_wait_kernel, dim3(1), dim3(64), 0, s, g.d_flag_slots, g.d_flags, g.d_epoch,
+                              g.d_error, g.n_ranks, limit_ns));
   return RI_OK;
 }
 

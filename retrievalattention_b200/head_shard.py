@@ -111,9 +111,9 @@ class HeadGather:
 
 class PeerGather:
     """The same gather without a collective: every rank's decode kernel stores its head slice straight
-    into the gather buffer of every rank of its group (peer-mapped memory over NVLink), and each of its
-    CTAs then writes the step's epoch into its flag word on every rank; ``wait(layer)`` enqueues a small
-    kernel that waits — with a time limit — until all flag words of that layer hold the epoch.
+    into the gather buffer of every rank of its group (peer-mapped memory over NVLink); ``wait(layer)``
+    enqueues, behind that kernel, a small one that writes the step's epoch into this rank's flag word on
+    every rank and then waits — with a time limit — until all ranks' flag words of that layer hold it.
 
     Buffers come from ``torch.distributed._symmetric_memory`` (one allocation per rank, mapped into
     every rank of ``group``).  NVLink multicast is not used (plain peer stores), and it is switched off
@@ -121,11 +121,11 @@ class PeerGather:
 
     Per step: ``next_step()`` once (advances the epoch), then per layer ``compute(..., gather=self)``
     and ``wait(layer)``.  Layout per rank: ``gathered[layer, shard, B, 1, Hq_local, d]`` and
-    ``flags[layer, shard, 8 * groups]``; ``view(layer)`` is the ``[B, 1, Hq, d]`` view of a layer.
+    ``flags[layer, shard]``; ``view(layer)`` is the ``[B, 1, Hq, d]`` view of a layer.
     """
 
     def __init__(self, shard: HeadShard, layers: int, batch: int, q_heads_local: int, head_dim: int,
-                 dtype: torch.dtype, device: torch.device, groups: int, group=None, wait_limit_us: int = 0):
+                 dtype: torch.dtype, device: torch.device, group=None, wait_limit_us: int = 0):
         import ctypes as C
         import os
 
@@ -137,11 +137,10 @@ class PeerGather:
         self.shard, self.layers = shard, layers
         n = shard.head_shards
         me = shard.head_index
-        n_flags = 8 * groups                      # CTAs of the decode kernel
         group = group if group is not None else dist.group.WORLD
         slice_elems = batch * q_heads_local * head_dim
         self.gathered = symm_mem.empty((layers, n, batch, 1, q_heads_local, head_dim), dtype=dtype, device=device)
-        self.flags = symm_mem.empty((layers, n, n_flags), dtype=torch.int32, device=device)
+        self.flags = symm_mem.empty((layers, n), dtype=torch.int32, device=device)
         self.gathered.zero_()
         self.flags.zero_()
         torch.cuda.synchronize(device)
@@ -154,7 +153,7 @@ class PeerGather:
         esz = self.gathered.element_size()
         out_slots = torch.tensor([[h_out.buffer_ptrs[p] + (l * n + me) * slice_elems * esz for p in range(n)]
                                   for l in range(layers)], dtype=torch.int64)
-        flag_slots = torch.tensor([[h_flag.buffer_ptrs[p] + (l * n + me) * n_flags * 4 for p in range(n)]
+        flag_slots = torch.tensor([[h_flag.buffer_ptrs[p] + (l * n + me) * 4 for p in range(n)]
                                    for l in range(layers)], dtype=torch.int64)
         self._out_slots = out_slots.to(device)
         self._flag_slots = flag_slots.to(device)
@@ -162,7 +161,7 @@ class PeerGather:
         self.params = []
         for l in range(layers):
             g = _lib.WaveGather()
-            g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = n, me, n_flags, wait_limit_us
+            g.n_ranks, g.rank, g.wait_limit_us = n, me, wait_limit_us
             g.d_out_slots = self._out_slots[l].data_ptr()
             g.d_flag_slots = self._flag_slots[l].data_ptr()
             g.d_flags = self.flags[l].data_ptr()

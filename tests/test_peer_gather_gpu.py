@@ -18,13 +18,13 @@ pytestmark = pytest.mark.gpu
 CASE = Case(2, 2, 4, 2048 + 68, 128, 1, 6, 30, seed=11)
 
 
-def make_gather(rank, n, n_flags, out_bufs, flag_bufs, epoch, error, limit_us, keep):
+def make_gather(rank, n, out_bufs, flag_bufs, epoch, error, limit_us, keep):
     slice_bytes = out_bufs[0][0].numel() * out_bufs[0].element_size()
     out_slots = torch.tensor([b.data_ptr() + rank * slice_bytes for b in out_bufs], dtype=torch.int64).cuda()
-    flag_slots = torch.tensor([f.data_ptr() + rank * n_flags * 4 for f in flag_bufs], dtype=torch.int64).cuda()
+    flag_slots = torch.tensor([f.data_ptr() + rank * 4 for f in flag_bufs], dtype=torch.int64).cuda()
     keep += [out_slots, flag_slots]
     g = _lib.WaveGather()
-    g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = n, rank, n_flags, limit_us
+    g.n_ranks, g.rank, g.wait_limit_us = n, rank, limit_us
     g.d_out_slots, g.d_flag_slots = out_slots.data_ptr(), flag_slots.data_ptr()
     g.d_flags = flag_bufs[rank].data_ptr()
     g.d_epoch, g.d_error = epoch.data_ptr(), error.data_ptr()
@@ -36,18 +36,22 @@ def test_two_ranks_on_one_gpu_fill_both_buffers_and_the_wait_returns():
     layers = [to_gpu_layer(CASE, cpu, SINK + RECENT, want_ids=False) for _ in range(2)]
     qs = [queries(CASE).cuda(), (queries(CASE) * 0.5).to(torch.bfloat16).cuda()]
     g_, gs = CASE.groups, CASE.group_size
-    n_flags = 8 * g_
     out_bufs = [torch.zeros((2, g_, gs, 128), dtype=torch.bfloat16, device="cuda") for _ in range(2)]   # per "rank"
-    flag_bufs = [torch.zeros((2, n_flags), dtype=torch.int32, device="cuda") for _ in range(2)]
+    flag_bufs = [torch.zeros((2,), dtype=torch.int32, device="cuda") for _ in range(2)]
     epoch = torch.zeros((1,), dtype=torch.int32, device="cuda")
     error = torch.zeros((1,), dtype=torch.int32, device="cuda")
     keep = []
-    gathers = [make_gather(r, 2, n_flags, out_bufs, flag_bufs, epoch, error, 200000, keep) for r in range(2)]
+    gathers = [make_gather(r, 2, out_bufs, flag_bufs, epoch, error, 3000, keep) for r in range(2)]
     for step in range(3):
         epoch.add_(1)
         outs = [layers[r].compute(qs[r], gather=gathers[r]).clone() for r in range(2)]
-        for r in range(2):
-            _lib.check(_lib.lib.ri_wave_gather_wait(C.byref(gathers[r]), _lib.current_stream()))
+        # "rank" 0 raises its flags and gives up waiting for rank 1's, which only the next call raises: on one
+        # GPU the two calls cannot run side by side, so the first wait must run out (and must not hang)
+        _lib.check(_lib.lib.ri_wave_gather_wait(C.byref(gathers[0]), _lib.current_stream()))
+        torch.cuda.synchronize()
+        assert int(error.item()) == 1
+        error.zero_()
+        _lib.check(_lib.lib.ri_wave_gather_wait(C.byref(gathers[1]), _lib.current_stream()))   # finds both flags
         torch.cuda.synchronize()
         assert int(error.item()) == 0
         for buf in out_bufs:                    # every rank's buffer holds both slices
@@ -61,13 +65,14 @@ def test_two_ranks_on_one_gpu_fill_both_buffers_and_the_wait_returns():
 
 
 def test_wait_gives_up_after_its_limit_and_reports_it():
-    flags = torch.zeros((2, 16), dtype=torch.int32, device="cuda")     # nothing ever raises these
+    flags = torch.zeros((2,), dtype=torch.int32, device="cuda")        # only this rank's own flag is ever raised
+    mine = torch.zeros((2,), dtype=torch.int32, device="cuda")
     epoch = torch.ones((1,), dtype=torch.int32, device="cuda")
     error = torch.zeros((1,), dtype=torch.int32, device="cuda")
-    dummy = torch.zeros((2,), dtype=torch.int64, device="cuda")
+    slots = torch.tensor([flags.data_ptr(), mine.data_ptr()], dtype=torch.int64).cuda()   # own flag here, peer's elsewhere
     g = _lib.WaveGather()
-    g.n_ranks, g.rank, g.n_flags, g.wait_limit_us = 2, 0, 16, 2000
-    g.d_out_slots = g.d_flag_slots = dummy.data_ptr()
+    g.n_ranks, g.rank, g.wait_limit_us = 2, 0, 2000
+    g.d_out_slots = g.d_flag_slots = slots.data_ptr()
     g.d_flags, g.d_epoch, g.d_error = flags.data_ptr(), epoch.data_ptr(), error.data_ptr()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -81,7 +86,7 @@ def test_wait_gives_up_after_its_limit_and_reports_it():
 
 def test_invalid_gather_arguments_are_rejected():
     g = _lib.WaveGather()
-    g.n_ranks, g.rank, g.n_flags = 1, 0, 8
+    g.n_ranks, g.rank = 1, 0
     assert _lib.lib.ri_wave_gather_wait(C.byref(g), None) != 0
     g.n_ranks, g.rank = 2, 5
     assert _lib.lib.ri_wave_gather_wait(C.byref(g), None) != 0
