@@ -595,18 +595,34 @@ struct BucketArgs {
   int64_t group_stride;
 };
 
-__global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a) {
-  extern __shared__ int32_t cursor[];   // [n_cen]: counts, then running write positions
+// One CTA per problem.  The tokens are cut into `workers` contiguous ranges; a table [workers][n_cen] first holds
+// how many tokens of each range fall into each cluster, then (after the scan of the totals) where each range
+// starts writing inside each cluster, so that `workers` warps can scatter their ranges side by side and the
+// order inside a cluster is still ascending in the token id.
+__global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a, int workers) {
+  extern __shared__ int32_t bucket_smem[];
+  int32_t* cursor = bucket_smem;                 // [n_cen]: counts, then first positions
+  int32_t* table = workers == 1 ? bucket_smem : bucket_smem + a.n_cen;   // [workers][n_cen]; one range: the same array
   __shared__ uint32_t warp_sums[32];
   __shared__ uint32_t s_carry;
   const int problem = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t tok0 = (int64_t)(problem / a.seg_per_group) * a.group_stride + (int64_t)(problem % a.seg_per_group) * a.n_tok;
   const int32_t* asg = a.assign + tok0;
-  for (int c = tid; c < a.n_cen; c += 1024) cursor[c] = 0;
+  const int chunk = ((a.n_tok + workers - 1) / workers + 31) & ~31;     // tokens per range, whole warp steps
+  for (int i = tid; i < a.n_cen * (workers == 1 ? 1 : workers + 1); i += 1024) bucket_smem[i] = 0;
   if (tid == 0) s_carry = 0;
   __syncthreads();
   auto clamp_id = [&](int32_t c) { return min(max(c, 0), a.n_cen - 1); };   // never index outside the table
-  for (int t = tid; t < a.n_tok; t += 1024) atomicAdd(&cursor[clamp_id(asg[t])], 1);
+  for (int t = tid; t < a.n_tok; t += 1024) {
+    const int c = clamp_id(asg[t]);
+    atomicAdd(&table[(t / chunk) * a.n_cen + c], 1);
+  }
+  __syncthreads();
+  for (int c = tid; c < a.n_cen; c += 1024) {
+    int total = 0;
+    for (int w = 0; w < workers; ++w) total += table[w * a.n_cen + c];
+    cursor[c] = total;
+  }
   __syncthreads();
   // exclusive scan of the counts, 1024 at a time
   for (int c0 = 0; c0 < a.n_cen; c0 += 1024) {
@@ -631,7 +647,13 @@ __global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a) {
     if (c < a.n_cen) {
       a.count[(int64_t)problem * a.n_cen + c] = (int32_t)v;
       a.offset[(int64_t)problem * (a.n_cen + 1) + c] = (int32_t)excl;
-      cursor[c] = (int32_t)excl;
+      // where each range starts inside this cluster
+      uint32_t running = excl;
+      for (int w = 0; w < workers; ++w) {
+        const int32_t n_w = table[w * a.n_cen + c];
+        table[w * a.n_cen + c] = (int32_t)running;
+        running += (uint32_t)n_w;
+      }
     }
     const uint32_t chunk_total = __shfl_sync(0xffffffffu, winc, 31);   // every lane takes part in the shuffle
     __syncthreads();
@@ -640,16 +662,18 @@ __global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a) {
   }
   if (tid == 0) a.offset[(int64_t)problem * (a.n_cen + 1) + a.n_cen] = (int32_t)s_carry;
   __syncthreads();
-  // stable scatter by one warp, 32 tokens at a time in token order
-  if (warp != 0) return;
+  // stable scatter: warp w takes range w, 32 tokens at a time in token order
+  if (warp >= workers) return;
   int32_t* ord = a.order + tok0;
+  int32_t* my_cursor = table + warp * a.n_cen;
+  const int t_begin = warp * chunk, t_end = min(a.n_tok, t_begin + chunk);
   constexpr int kAhead = 8;
-  for (int t0 = 0; t0 < a.n_tok; t0 += 32 * kAhead) {
+  for (int t0 = t_begin; t0 < t_end; t0 += 32 * kAhead) {
     int32_t cl[kAhead];
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
       const int t = t0 + u * 32 + lane;
-      cl[u] = t < a.n_tok ? clamp_id(asg[t]) : -1;
+      cl[u] = t < t_end ? clamp_id(asg[t]) : -1;
     }
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
@@ -658,10 +682,10 @@ __global__ void __launch_bounds__(1024) kmeans_bucket_kernel(BucketArgs a) {
       if (cl[u] >= 0) {
         const unsigned peers = __match_any_sync(active, cl[u]);
         const int rank = __popc(peers & ((1u << lane) - 1u));
-        const int pos = cursor[cl[u]] + rank;
+        const int pos = my_cursor[cl[u]] + rank;
         ord[pos] = t;
         __syncwarp(active);
-        if (lane == 31 - __clz(peers)) cursor[cl[u]] = pos + 1;
+        if (lane == 31 - __clz(peers)) my_cursor[cl[u]] = pos + 1;
       }
       __syncwarp();
     }
@@ -711,30 +735,35 @@ __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
 
   float ks[4] = {0, 0, 0, 0}, vs[4] = {0, 0, 0, 0};
   constexpr int kUnroll = 4;
-  for (int j0 = 0; j0 < cnt; j0 += kUnroll) {
-    int rows[kUnroll];
-    uint2 kv[kUnroll], vv[kUnroll], rk[kUnroll];
+  for (int b0 = 0; b0 < cnt; b0 += 32) {
+    // the member list of up to 32 rows in one coalesced load; the rows are then fetched kUnroll at a time
+    const int my_row = b0 + lane < cnt ? ord[b0 + lane] : -1;
+    const int n_here = min(32, cnt - b0);
+    for (int j0 = 0; j0 < n_here; j0 += kUnroll) {
+      int rows[kUnroll];
+      uint2 kv[kUnroll], vv[kUnroll], rk[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) rows[u] = j0 + u < cnt ? ord[j0 + u] : -1;
+      for (int u = 0; u < kUnroll; ++u) rows[u] = __shfl_sync(0xffffffffu, my_row, (j0 + u) & 31);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
-      if (rows[u] >= 0) {
-        const int64_t r = (tok0 + rows[u]) * 32 + lane;
-        kv[u] = __ldg(a.centred + r);
-        if (a.values) vv[u] = __ldg(a.values + r);
-        if (a.raw_keys) rk[u] = __ldg(a.raw_keys + r);
-      }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
-      if (rows[u] >= 0) {
-        add_row<DT>(ks, kv[u]);           // sequential in list order: bit-identical to a serial sum
-        if (a.values) add_row<DT>(vs, vv[u]);
-        if (a.keys_out) {
-          const int64_t o = ((int64_t)z * a.group_stride + off + j0 + u) * 32 + lane;
-          a.keys_out[o] = rk[u];
-          a.values_out[o] = vv[u];
+      for (int u = 0; u < kUnroll; ++u)
+        if (j0 + u < n_here) {
+          const int64_t r = (tok0 + rows[u]) * 32 + lane;
+          kv[u] = __ldg(a.centred + r);
+          if (a.values) vv[u] = __ldg(a.values + r);
+          if (a.raw_keys) rk[u] = __ldg(a.raw_keys + r);
         }
-      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (j0 + u < n_here) {
+          add_row<DT>(ks, kv[u]);           // sequential in list order: bit-identical to a serial sum
+          if (a.values) add_row<DT>(vs, vv[u]);
+          if (a.keys_out) {
+            const int64_t o = ((int64_t)z * a.group_stride + off + b0 + j0 + u) * 32 + lane;
+            a.keys_out[o] = rk[u];
+            a.values_out[o] = vv[u];
+          }
+        }
+    }
   }
   if (a.value_sum) {
     uint2 o;
@@ -922,10 +951,14 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
     ba.count = last && p->d_cluster_count ? p->d_cluster_count : count_work;
     ba.offset = last && p->d_cluster_offset ? p->d_cluster_offset : offset_work;
     ba.n_tok = n_tok; ba.n_cen = n_cen; ba.seg_per_group = seg; ba.group_stride = N;
-    const size_t bsmem = (size_t)n_cen * 4;
+    // as many token ranges (scattering warps) as fit the shared memory: a table of [ranges + 1][n_cen] words
+    int workers = 32;
+    while (workers > 1 && (size_t)(workers + 1) * n_cen * 4 > 200 * 1024) workers >>= 1;
+    const size_t bsmem = (size_t)(workers == 1 ? 1 : workers + 1) * n_cen * 4;
+    RI_REQUIRE(bsmem <= 227 * 1024, "n_centroids per problem = %d too large for the bucket pass", n_cen);
     if (bsmem > 48 * 1024)
       RI_CUDA_OK(cudaFuncSetAttribute(kmeans_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
-    kmeans_bucket_kernel<<<problems, 1024, bsmem, s>>>(ba);
+    kmeans_bucket_kernel<<<problems, 1024, bsmem, s>>>(ba, workers);
     RI_LAUNCH_OK("kmeans_bucket_kernel");
     if ((rc0 = trace_stage("bucket", s)) != RI_OK) return rc0;
 

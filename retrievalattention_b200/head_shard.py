@@ -119,6 +119,10 @@ class PeerGather:
     every rank of ``group``).  NVLink multicast is not used (plain peer stores), and it is switched off
     for the allocation so that no rank's memory is bound to a multicast object.
 
+    A rank may overwrite layer l's slice on its peers as soon as their NEXT wait of any layer has passed, so a
+    consumer must have read ``view(l)`` before its rank enqueues the wait after next — automatic with two or more
+    layers consumed in order; a single-layer model needs two ``PeerGather`` objects used alternately.
+
     Per step: ``next_step()`` once (advances the epoch), then per layer ``compute(..., gather=self)``
     and ``wait(layer)``.  Layout per rank: ``gathered[layer, shard, B, 1, Hq_local, d]`` and
     ``flags[layer, shard]``; ``view(layer)`` is the ``[B, 1, Hq, d]`` view of a layer.
