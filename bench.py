@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Decode-throughput benchmark of the wave-index attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config cfg1|cfg2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config cfg1|cfg2] [--with-model]
 
 Workload (default, N=1): Llama-3-8B decode-attention geometry — 32 layers, 32 q / 8 kv heads,
 head_dim 128, batch 4, context 131072, 8192 centroids per kv head, budget 0.018, estimate 0.232 —
@@ -291,6 +291,64 @@ def cpu_layer_seconds(wl, layer_idx, step, repeats):
     return statistics.median(times[1:])
 
 
+def model_decode(wl, geo, args, warm, log):
+    """Decode tokens/s of the whole model step around the same caches (``--with-model``): embedding,
+    per layer RMS norm -> fused QKV projection -> rotary embedding -> cache update + wave-index
+    attention -> output projection -> RMS norm -> MLP, final norm, vocabulary projection and greedy
+    arg-max, with seeded random weights at the model's published shapes; one CUDA graph per step.
+    The second figure feeds the token ids from pinned host memory and reads the next ids back every step."""
+    from retrievalattention_b200 import decode_layer as dl
+
+    shapes = {"llama3-8b": dl.LLAMA3_8B, "qwen2.5-7b": dl.QWEN25_7B, "qwen2.5-72b": dl.QWEN25_72B}
+    shape = next((v for k, v in shapes.items() if geo.name.startswith(k)), None)
+    if shape is None:
+        return {"unavailable": f"no model shape for {geo.name}"}
+    need = shape.layers * (shape.qkv_dim + shape.q_heads * 128 + 3 * shape.intermediate) * shape.hidden * 2 \
+        + 2 * shape.vocab * shape.hidden * 2
+    free = torch.cuda.mem_get_info(wl.device)[0]
+    if need > free - (4 << 30):
+        return {"unavailable": f"weights need {need / 2**30:.0f} GiB, {free / 2**30:.0f} GiB free on this GPU"}
+    dec = dl.SyntheticDecoder(replace(shape, layers=geo.layers), wl.cache, geo.batch, geo.context + 4096, wl.device)
+    dec.positions.fill_(geo.context + wl.static_len() - (SINK + RECENT + 1))
+    dec.decode_forward()                                   # eager once, then captured
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        dec.decode_forward()
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    ids_host = torch.randint(0, shape.vocab, (warm + args.steps, geo.batch), dtype=torch.int64).pin_memory()
+    next_host = torch.zeros((geo.batch,), dtype=torch.int64).pin_memory()
+
+    def run(first, count):
+        for st in range(first, first + count):
+            dec.input_ids.copy_(ids_host[st], non_blocking=True)
+            graph.replay()
+            next_host.copy_(dec.next_ids, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    run(0, warm)
+    e0.record()
+    run(warm, args.steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    log(f"model step: {ms:.3f} ms resident, {ms_e2e:.3f} ms with host ids")
+    return {"model": f"{geo.name.split('-128k')[0]} shapes, random-init bf16 weights (std 0.02)",
+            "tok_s": round(geo.batch / ms * 1e3, 1), "ms_per_step": round(ms, 4),
+            "e2e_tok_s": round(geo.batch / ms_e2e * 1e3, 1), "weight_bytes_per_step": dec.weight_bytes_per_step(),
+            "launches_per_step": 9 * geo.layers + 7,
+            "note": "per layer: 3 of this library's element-wise kernels + the decode kernel + 4 library GEMMs"}
+
+
 # ----------------------------------------------------------------------------------------------
 # decode benchmark
 # ----------------------------------------------------------------------------------------------
@@ -311,6 +369,8 @@ def run_decode(geo, args, rank, world, local_rank, log):
     warm = max(args.warmup, 3)
     stage_steps = min(args.steps, 4)
     total = 2 * (warm + args.steps) + stage_steps + 2
+    if args.with_model:
+        total += 2 * (warm + args.steps) + 2      # the model run appends to the same steady zones
     wl = Workload(geo, device, total, args.kmeans_iters, rank, log, world)
     wl.capture()      # consumes 2 steps of the steady zone
 
@@ -438,6 +498,12 @@ def run_decode(geo, args, rank, world, local_rank, log):
                      "path": {"alg_bytes_per_step": int(step_alg), "gbs": round(step_alg / (ms / args.steps) / 1e6, 1),
                               "frac": round(step_alg / (ms / args.steps) / 1e6 / peak, 4)}},
     }
+    if args.with_model and world == 1:
+        result["decode_model"] = model_decode(wl, geo, args, warm, log)
+        mb = result["decode_model"].get("weight_bytes_per_step")
+        if mb:
+            gbs = (mb + step_alg) / result["decode_model"]["ms_per_step"] / 1e6
+            result["decode_model"].update({"gbs": round(gbs, 1), "frac": round(gbs / peak, 4)})
     if not args.no_cpu_baseline:
         sec = cpu_layer_seconds(wl, 0, warm, 2)
         result["cpu_baseline"] = {"value": round(geo.batch / (sec * geo.layers), 3), "unit": "tok/s",
@@ -547,6 +613,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override layer count (profiling on a small case only)")
     ap.add_argument("--kmeans-iters", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--with-model", action="store_true",
+                    help="also time the whole model decode step (projections, MLP, vocabulary head with random weights) "
+                         "around the same caches; adds the key decode_model (single GPU)")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
     args = ap.parse_args()
 

@@ -169,6 +169,33 @@ int ri_steady_append(const void* d_k, const void* d_v, void* d_steady_keys, void
                      const int32_t* d_position, int32_t groups, int32_t steady_stride, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Element-wise kernels of the decode layer around the attention (the caller of this path,
+ * model_hub/LLM.py:90-126 `layer_decode`).  The projections stay library GEMMs; these three
+ * replace the flashinfer calls between them.  Rows = batch (one token per request).
+ * ------------------------------------------------------------------------------------------ */
+
+/* out = rmsnorm(h) * weight with h = x, or, when d_residual is given, h = d_residual + x rounded
+ * to `dtype` and written back to d_residual first.  Replaces flashinfer.rmsnorm
+ * (model_hub/llama.py:304-309) and the residual additions of LLM.py:118-119, :124.
+ * d_x, d_residual, d_out: [rows, dim]; d_weight: [dim]; dim a multiple of 8, <= 16384. */
+int ri_rmsnorm(const void* d_x, void* d_residual, const void* d_weight, void* d_out, int32_t rows,
+               int32_t dim, float eps, int32_t dtype, void* stream);
+
+/* Rotary embedding (first-half/second-half pairing) of the query and key heads of a fused QKV
+ * projection, and its split into contiguous tensors.  Replaces the split of model_hub/llama.py:232-235
+ * and flashinfer.rope.apply_rope_with_cos_sin_cache_inplace(..., is_neox=True) (:312-320).
+ * d_qkv: [rows, (q_heads + 2*kv_heads) * 128]; d_cos_sin: fp32 [max_positions, 128], cosines in
+ * columns 0..63, sines in 64..127 (:81-84, :109); d_positions: [rows] int64, read on the device
+ * (values outside [0, max_positions) are clamped); d_q: [rows, q_heads, 128]; d_k, d_v: [rows, kv_heads, 128]. */
+int ri_rope_split(const void* d_qkv, const float* d_cos_sin, const int64_t* d_positions, void* d_q,
+                  void* d_k, void* d_v, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                  int64_t max_positions, int32_t dtype, void* stream);
+
+/* out[r, j] = silu(in[r, j]) * in[r, inter + j].  Replaces flashinfer.activation.silu_and_mul
+ * (model_hub/llama.py:267-275).  d_in: [rows, 2*inter]; d_out: [rows, inter]; inter a multiple of 8. */
+int ri_silu_and_mul(const void* d_in, void* d_out, int32_t rows, int32_t inter, int32_t dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Prefill clustering.  Replaces cache_hub/kmeans.py:224-259 (`segment_k_means`: Triton assign,
  * update, index-add and reverse-index kernels) and, with `center` = 1, also its caller's
  * wrapping in cache_hub/retroinfer_cache.py:416-432 (mean-centring, centroid + mean, sizes in

@@ -115,6 +115,12 @@ def _load() -> C.CDLL:
                                                                   C.c_int32, C.c_int32, C.c_void_p])
     lib.ri_gather_copy_and_scatter.restype = C.c_int
     lib.ri_gather_copy_and_scatter.argtypes = [C.c_void_p] * 8 + [C.c_int32] * 5 + [C.c_void_p]
+    lib.ri_rmsnorm.restype = C.c_int
+    lib.ri_rmsnorm.argtypes = [C.c_void_p] * 4 + [C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_void_p]
+    lib.ri_rope_split.restype = C.c_int
+    lib.ri_rope_split.argtypes = [C.c_void_p] * 6 + [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_void_p]
+    lib.ri_silu_and_mul.restype = C.c_int
+    lib.ri_silu_and_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.ri_steady_append.restype = C.c_int
     lib.ri_steady_append.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_int32, C.c_void_p]
     return lib
