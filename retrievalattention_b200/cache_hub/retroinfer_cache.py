@@ -20,6 +20,9 @@ offload, no CPU re-layout).  Two storage tiers:
   pages straight from pinned memory, the attend stage runs on the execution buffer, and
   ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
 
+After every 1024 generated tokens ``decode_update_kv_cache`` folds them into the index (``_update_kv_cache``,
+:462-524), provided ``max_new_length`` announced that many at construction (HBM tier).
+
 ``use_cluster_estimation`` is accepted for compatibility and ignored.
 """
 from __future__ import annotations
@@ -63,6 +66,10 @@ class retroinfer_cache(KV_Cache):
 
         self.input_length = max_length - max_new_length
         self.max_new_length = min(max_new_length - 1, THRESHOLD_LENGTH)       # :64
+        # re-indexing of generated tokens (:66-69): every THRESHOLD_LENGTH of them become 64 more clusters
+        self.input_length_new = max(0, (max_new_length - 2) // THRESHOLD_LENGTH) * THRESHOLD_LENGTH
+        self.n_centroids_per_update_segment = ((THRESHOLD_LENGTH // 16) // 32) * 32
+        self.n_centroids_new = max(0, (max_new_length - 2) // THRESHOLD_LENGTH) * self.n_centroids_per_update_segment
         self.static_stride = self.static_pattern_total + self.max_new_length
         self.n_centroids = n_centroids
         self.n_segment = n_segment
@@ -73,7 +80,8 @@ class retroinfer_cache(KV_Cache):
         pages_per_cluster = math.ceil(avg_cluster_size / self.page_size)
         self.cache_size = cache_cluster_num * pages_per_cluster
         self.buffer_size = max(int(nprobe * 4), 16) * pages_per_cluster      # :111, page budget per group
-        self.list_stride = self.input_length - self.static_pattern_total
+        # rows of the cluster store per group: the prompt's clustered tokens, then room for the re-indexed ones (:264-274)
+        self.list_stride = self.input_length - self.static_pattern_total + self.input_length_new
 
         self.kv_on_host = bool(kv_on_host)
         g, c, d = self.batch_groups, n_centroids, head_dim
@@ -104,6 +112,7 @@ class retroinfer_cache(KV_Cache):
 
         self.shape = wave.WaveShape(g, self.group_size, c, nprobe, self.es_cluster_num, self.page_size,
                                     self.buffer_size, self.list_stride, self.static_stride, dtype)
+        self.reindex_count = 0
         # per device: scratch shared by the layers of that device, and the device-side counters
         self._per_device = {}
         for dev in sorted(set(layer_mapping.values())):
@@ -221,12 +230,61 @@ class retroinfer_cache(KV_Cache):
                 steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
                 static_len=per["static_len"], scratch=per["scratch"])
 
+    # ------------------------------------------------------------------ re-index
+    def _update_kv_cache(self):
+        """Fold the THRESHOLD_LENGTH oldest tokens of the steady zone's tail into the wave index (:462-524):
+        cluster them per group into ``n_centroids_per_update_segment`` more clusters (one segment, keys
+        centred on their own mean), append centroids / value sums / sizes to the meta index and the
+        members, cluster-contiguous, to the cluster store, then move the last ``static_pattern_end`` rows
+        down behind the sink tokens.  Everything stays on the device (the reference offloads the rows to
+        the host and re-lays them out there).  Tensors of the meta index are replaced by longer ones, so a
+        CUDA graph captured before this call no longer describes the cache and has to be captured again."""
+        if self.kv_on_host:
+            raise NotImplementedError("re-indexing of generated tokens is built for the HBM tier only")
+        if (self.reindex_count + 1) * THRESHOLD_LENGTH > self.input_length_new:
+            raise RuntimeError("the cluster store has no room left for re-indexed tokens (max_new_length too small)")
+        start, end, total = self.static_pattern_start, self.static_pattern_end, self.static_pattern_total
+        g, d, extra = self.batch_groups, self.head_dim, self.n_centroids_per_update_segment
+        for ldx in range(self.layer_num):
+            dev = self.layer_mapping[str(ldx)]
+            with torch.cuda.device(dev):
+                sk, sv = self.steady_zone_keys[ldx], self.steady_zone_values[ldx]
+                update_keys = sk[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).contiguous()
+                update_values = sv[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).contiguous()
+                tail_k, tail_v = sk[:, :, total - end:total].clone(), sv[:, :, total - end:total].clone()
+                sk[:, :, start:start + end] = tail_k        # move the local window (:469-472)
+                sv[:, :, start:start + end] = tail_v
+                r = build_index(update_keys, update_values, extra, 1)
+                self._error_flags.append(r["error"])
+                old_off = self.cluster_offset[ldx]
+                first = old_off[:, -1:].long()               # rows already used by each group
+                self.centroids[ldx] = torch.cat((self.centroids[ldx], r["centroids"]), dim=1)
+                self.value_sum[ldx] = torch.cat((self.value_sum[ldx], r["value_sum"]), dim=1)
+                self.cluster_size[ldx] = torch.cat((self.cluster_size[ldx], r["cluster_size"]), dim=1)
+                self.cluster_count[ldx] = torch.cat((self.cluster_count[ldx], r["cluster_count"]), dim=1)
+                self.centroids_mask[ldx] = torch.cat((self.centroids_mask[ldx], r["cluster_count"] == 0), dim=1)
+                self.cluster_offset[ldx] = torch.cat((old_off, (first + r["cluster_offset"][:, 1:].long()).to(torch.int32)),
+                                                     dim=1)
+                rows = first + torch.arange(THRESHOLD_LENGTH, device=dev)[None, :]
+                pick = torch.arange(g, device=dev)[:, None]
+                self.list_keys[ldx].view(g, self.list_stride, d)[pick, rows] = r["keys"]
+                self.list_values[ldx].view(g, self.list_stride, d)[pick, rows] = r["values"]
+        self.n_centroids += extra                            # :509
+        self.reindex_count += 1
+        self.static_pattern_total = start + end              # :522
+        self.shape = wave.WaveShape(g, self.group_size, self.n_centroids, self.nprobe, self.es_cluster_num,
+                                    self.page_size, self.buffer_size, self.list_stride, self.static_stride, self.dtype)
+        for dev, per in self._per_device.items():
+            per["scratch"] = wave.new_scratch(self.shape, dev)
+            per["static_len"].fill_(self.static_pattern_total + 1)
+            per["append_pos"].fill_(self.static_pattern_total)
+        self.prepare_cache()
+
     # ------------------------------------------------------------------ decode
     def decode_update_kv_cache(self, key_states, value_states, layer_idx):
         """Append the new token's K/V ([bs, 1, kv_heads, d]) to the steady zone (:527-546)."""
         if self.static_pattern_total == self.static_pattern_start + self.static_pattern_end + THRESHOLD_LENGTH:
-            raise NotImplementedError(
-                "re-indexing after 1024 generated tokens (reference _update_kv_cache, :462-524) is not built yet")
+            self._update_kv_cache()
         per = self._per_device[self.layer_mapping[str(layer_idx)]]
         g = self.batch_groups
         if self.fuse_append:
