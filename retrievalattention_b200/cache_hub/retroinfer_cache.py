@@ -21,7 +21,7 @@ offload, no CPU re-layout).  Two storage tiers:
   ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
 
 After every 1024 generated tokens ``decode_update_kv_cache`` folds them into the index (``_update_kv_cache``,
-:462-524), provided ``max_new_length`` announced that many at construction (HBM tier).
+:462-524), provided ``max_new_length`` announced that many at construction.
 
 ``use_cluster_estimation`` is accepted for compatibility and ignored.
 """
@@ -142,7 +142,8 @@ class retroinfer_cache(KV_Cache):
             self.cache_keys.append(torch.zeros((g, self.cache_size, self.page_size, d), dtype=self.dtype, device=dev))
             self.cache_values.append(torch.zeros((g, self.cache_size, self.page_size, d), dtype=self.dtype, device=dev))
             wb = WaveBufferCPU(self.batch_size, self.kv_head, d, self.nprobe, self.page_size, self.n_centroids,
-                               self.n_centroids, self.buffer_size, self.cache_size, self.core, self.thread_pool.get())
+                               self.n_centroids + self.n_centroids_new, self.buffer_size, self.cache_size, self.core,
+                               self.thread_pool.get())
             b = self.buffer_size
             lists = [i32(g, b), i32(g, b), i32(g, b), i32(g), i32(g, b), i32(g, b), i32(g, b), i32(g),
                      i32(g, b), i32(g, b), i32(g, b), i32(g)]
@@ -236,11 +237,10 @@ class retroinfer_cache(KV_Cache):
         cluster them per group into ``n_centroids_per_update_segment`` more clusters (one segment, keys
         centred on their own mean), append centroids / value sums / sizes to the meta index and the
         members, cluster-contiguous, to the cluster store, then move the last ``static_pattern_end`` rows
-        down behind the sink tokens.  Everything stays on the device (the reference offloads the rows to
-        the host and re-lays them out there).  Tensors of the meta index are replaced by longer ones, so a
+        down behind the sink tokens.  The clustering and the re-layout run on the device (the reference offloads
+        the rows to the host and re-lays them out there); on the host tier the laid-out members are then copied
+        into the pinned cluster store.  Tensors of the meta index are replaced by longer ones, so a
         CUDA graph captured before this call no longer describes the cache and has to be captured again."""
-        if self.kv_on_host:
-            raise NotImplementedError("re-indexing of generated tokens is built for the HBM tier only")
         if (self.reindex_count + 1) * THRESHOLD_LENGTH > self.input_length_new:
             raise RuntimeError("the cluster store has no room left for re-indexed tokens (max_new_length too small)")
         start, end, total = self.static_pattern_start, self.static_pattern_end, self.static_pattern_total
@@ -265,10 +265,20 @@ class retroinfer_cache(KV_Cache):
                 self.centroids_mask[ldx] = torch.cat((self.centroids_mask[ldx], r["cluster_count"] == 0), dim=1)
                 self.cluster_offset[ldx] = torch.cat((old_off, (first + r["cluster_offset"][:, 1:].long()).to(torch.int32)),
                                                      dim=1)
-                rows = first + torch.arange(THRESHOLD_LENGTH, device=dev)[None, :]
-                pick = torch.arange(g, device=dev)[:, None]
-                self.list_keys[ldx].view(g, self.list_stride, d)[pick, rows] = r["keys"]
-                self.list_values[ldx].view(g, self.list_stride, d)[pick, rows] = r["values"]
+                if self.kv_on_host:
+                    # cluster store in pinned host memory: the members go behind each group's rows there, and the
+                    # host wave buffer learns the new clusters' sizes (wave_buffer_cpu.cpp:635-720 `update_kv`)
+                    lk = self.list_keys[ldx].view(g, self.list_stride, d)
+                    lv = self.list_values[ldx].view(g, self.list_stride, d)
+                    for grp, n0 in enumerate(first.view(-1).tolist()):
+                        lk[grp, n0:n0 + THRESHOLD_LENGTH].copy_(r["keys"][grp])
+                        lv[grp, n0:n0 + THRESHOLD_LENGTH].copy_(r["values"][grp])
+                    self.wave_buffer[ldx].update_kv(None, None, None, r["cluster_count"])
+                else:
+                    rows = first + torch.arange(THRESHOLD_LENGTH, device=dev)[None, :]
+                    pick = torch.arange(g, device=dev)[:, None]
+                    self.list_keys[ldx].view(g, self.list_stride, d)[pick, rows] = r["keys"]
+                    self.list_values[ldx].view(g, self.list_stride, d)[pick, rows] = r["values"]
         self.n_centroids += extra                            # :509
         self.reindex_count += 1
         self.static_pattern_total = start + end              # :522

@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 THRESHOLD = 1024
 
 
-def test_reindex_after_1024_generated_tokens():
+@pytest.mark.parametrize("kv_on_host", [False, True], ids=["hbm_tier", "host_tier"])
+def test_reindex_after_1024_generated_tokens(kv_on_host):
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
     batch, layers, kv_heads, q_heads, seq_len = 2, 2, 2, 8, 1024 + 68
@@ -27,7 +28,7 @@ def test_reindex_after_1024_generated_tokens():
     cfg = generate_config(seq_len, 0.05, 0.2, n_segments=1)
     mapping = {str(l): "cuda:0" for l in range(layers)}
     cache = retroinfer_cache(valid_start, layers, batch, seq_len + max_new, kv_heads, q_heads, 128, torch.bfloat16,
-                             mapping, max_new, num_gpus=1, model_size=8, **cfg.as_kwargs())
+                             mapping, max_new, num_gpus=1, model_size=8, kv_on_host=kv_on_host, **cfg.as_kwargs())
     assert cache.input_length_new == THRESHOLD and cache.n_centroids_per_update_segment == 64
     for b in range(batch):
         for l in range(layers):
@@ -72,8 +73,8 @@ def test_reindex_after_1024_generated_tokens():
         # local window moved behind the sink tokens; the new token follows it
         assert torch.equal(cache.steady_zone_keys[l][:, :, 4:68], old_keys[l][:, :, 68 + THRESHOLD - 64:68 + THRESHOLD])
         assert torch.equal(cache.steady_zone_values[l][:, :, 4:68], old_values[l][:, :, 68 + THRESHOLD - 64:68 + THRESHOLD])
-        lk = cache.list_keys[l].view(g, -1, 128)
-        lv = cache.list_values[l].view(g, -1, 128)
+        lk = cache.list_keys[l].view(g, -1, 128).cuda()        # pinned host memory on the host tier
+        lv = cache.list_values[l].view(g, -1, 128).cuda()
         moved_k = old_keys[l].view(g, -1, 128)[:, 4:4 + THRESHOLD]
         moved_v = old_values[l].view(g, -1, 128)[:, 4:4 + THRESHOLD]
         for grp in range(g):
