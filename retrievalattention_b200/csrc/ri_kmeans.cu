@@ -719,12 +719,19 @@ __device__ __forceinline__ void add_row(float (&acc)[4], uint2 v) {
   acc[3] += Elem<DT>::from_bits((uint16_t)(v.y >> 16));
 }
 
-template <int DT>
-__global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
-  const int problem = blockIdx.y;
+// LAST: the pass that also sums the values and writes the cluster-contiguous copy (three rows per member).
+// Cluster sizes are very uneven (median of a few members, a tail of thousands).  With one short-lived CTA per
+// eight clusters most CTAs had next to nothing to do and the kernel was bound by CTA turnover (about 220 CTAs
+// per SM in a row), so the warps are persistent instead: a few CTAs per SM, warp w of the grid takes clusters
+// w, w + W, w + 2W, ... of all problems, which also evens out the large clusters.
+template <int DT, bool LAST>
+__global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a, int n_problems) {
   const int lane = threadIdx.x & 31;
-  const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (c >= a.n_cen) return;
+  const int64_t n_total = (int64_t)n_problems * a.n_cen;
+  const int64_t n_warps = (int64_t)gridDim.x * 8;
+  for (int64_t idx = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); idx < n_total; idx += n_warps) {
+  const int problem = (int)(idx / a.n_cen);
+  const int c = (int)(idx - (int64_t)problem * a.n_cen);
   const int z = problem / a.seg_per_group;
   const int64_t tok0 = (int64_t)z * a.group_stride + (int64_t)(problem % a.seg_per_group) * a.n_tok;
   const int cnt = a.count[(int64_t)problem * a.n_cen + c];
@@ -734,7 +741,7 @@ __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
   if (a.size_dt) a.size_dt[(int64_t)problem * a.n_cen + c] = Elem<DT>::bits((float)cnt);
 
   float ks[4] = {0, 0, 0, 0}, vs[4] = {0, 0, 0, 0};
-  constexpr int kUnroll = 4;
+  constexpr int kUnroll = LAST ? 8 : 4;
   for (int b0 = 0; b0 < cnt; b0 += 32) {
     // the member list of up to 32 rows in one coalesced load; the rows are then fetched kUnroll at a time
     const int my_row = b0 + lane < cnt ? ord[b0 + lane] : -1;
@@ -749,15 +756,15 @@ __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
         if (j0 + u < n_here) {
           const int64_t r = (tok0 + rows[u]) * 32 + lane;
           kv[u] = __ldg(a.centred + r);
-          if (a.values) vv[u] = __ldg(a.values + r);
-          if (a.raw_keys) rk[u] = __ldg(a.raw_keys + r);
+          if (LAST && a.values) vv[u] = __ldg(a.values + r);
+          if (LAST && a.raw_keys) rk[u] = __ldg(a.raw_keys + r);
         }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
         if (j0 + u < n_here) {
           add_row<DT>(ks, kv[u]);           // sequential in list order: bit-identical to a serial sum
-          if (a.values) add_row<DT>(vs, vv[u]);
-          if (a.keys_out) {
+          if (LAST && a.values) add_row<DT>(vs, vv[u]);
+          if (LAST && a.keys_out) {
             const int64_t o = ((int64_t)z * a.group_stride + off + b0 + j0 + u) * 32 + lane;
             a.keys_out[o] = rk[u];
             a.values_out[o] = vv[u];
@@ -801,6 +808,7 @@ __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a) {
                           Elem<DT>::from_bits((uint16_t)(cd.y >> 16)) + Elem<DT>::from_bits((uint16_t)(m.y >> 16)));
     a.out_centroids[crow] = o;
   }
+  }   // next cluster of this warp
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -981,8 +989,21 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
         ua.out_centroids = static_cast<uint2*>(p->d_centroids);
       }
     }
-    dim3 ugrid((n_cen + 7) / 8, problems);
-    kmeans_update_kernel<DT><<<ugrid, 256, 0, s>>>(ua);
+    // persistent warps: as many CTAs as are resident at once
+    static int resident[2] = {0, 0};
+    const int form = ua.values ? 1 : 0;
+    if (resident[form] == 0) {
+      int per_sm = 0, sms = 0, dev = 0;
+      RI_CUDA_OK(cudaGetDevice(&dev));
+      RI_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      if (form) RI_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kmeans_update_kernel<DT, true>, 256, 0));
+      else RI_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kmeans_update_kernel<DT, false>, 256, 0));
+      resident[form] = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 148);
+    }
+    const int64_t ctas_needed = ((int64_t)n_cen * problems + 7) / 8;
+    const int ugrid = (int)(ctas_needed < resident[form] ? ctas_needed : resident[form]);
+    if (form) kmeans_update_kernel<DT, true><<<ugrid, 256, 0, s>>>(ua, problems);
+    else kmeans_update_kernel<DT, false><<<ugrid, 256, 0, s>>>(ua, problems);
     RI_LAUNCH_OK("kmeans_update_kernel");
     if ((rc0 = trace_stage("update", s)) != RI_OK) return rc0;
   }
