@@ -727,13 +727,17 @@ __device__ __forceinline__ void add_row(float (&acc)[4], uint2 v) {
 template <int DT, bool LAST>
 __global__ void __launch_bounds__(256) kmeans_update_kernel(UpdateArgs a, int n_problems) {
   const int lane = threadIdx.x & 31;
-  const int64_t n_total = (int64_t)n_problems * a.n_cen;
-  const int64_t n_warps = (int64_t)gridDim.x * 8;
-  for (int64_t idx = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); idx < n_total; idx += n_warps) {
-  const int problem = (int)(idx / a.n_cen);
-  const int c = (int)(idx - (int64_t)problem * a.n_cen);
-  const int z = problem / a.seg_per_group;
-  const int64_t tok0 = (int64_t)z * a.group_stride + (int64_t)(problem % a.seg_per_group) * a.n_tok;
+  // most clusters hold a handful of rows, so the per-cluster index arithmetic counts: 32-bit, and (problem, c)
+  // advance by a fixed step instead of being divided out of the running index (the launcher checks the range)
+  const int n_total = n_problems * a.n_cen;
+  const int n_warps = (int)gridDim.x * 8;
+  const int step_p = n_warps / a.n_cen, step_c = n_warps - step_p * a.n_cen;
+  const int idx0 = (int)blockIdx.x * 8 + (int)(threadIdx.x >> 5);
+  int problem = idx0 / a.n_cen, c = idx0 - problem * a.n_cen;
+  for (int idx = idx0; idx < n_total; idx += n_warps, problem += step_p, c += step_c) {
+  if (c >= a.n_cen) { c -= a.n_cen; ++problem; }
+  const int z = (int)((unsigned)problem / (unsigned)a.seg_per_group);
+  const int64_t tok0 = (int64_t)z * a.group_stride + (int64_t)(problem - z * a.seg_per_group) * a.n_tok;
   const int cnt = a.count[(int64_t)problem * a.n_cen + c];
   const int off = a.offset[(int64_t)problem * (a.n_cen + 1) + c];
   const int32_t* ord = a.order + tok0 + off;
@@ -1000,6 +1004,7 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
       else RI_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kmeans_update_kernel<DT, false>, 256, 0));
       resident[form] = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : 148);
     }
+    RI_REQUIRE((int64_t)n_cen * problems < (1ll << 30), "too many clusters in one launch (%d x %d)", n_cen, problems);
     const int64_t ctas_needed = ((int64_t)n_cen * problems + 7) / 8;
     const int ugrid = (int)(ctas_needed < resident[form] ? ctas_needed : resident[form]);
     if (form) kmeans_update_kernel<DT, true><<<ugrid, 256, 0, s>>>(ua, problems);
