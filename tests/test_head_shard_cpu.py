@@ -59,7 +59,7 @@ def _worker(rank, world, port, ret):
 
 def test_head_sharded_attention_equals_single_rank():
     world, port = 2, _free_port()
-    with mp.Manager() as m:
+    with mp.get_context("spawn").Manager() as m:
         ret = m.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert ret["equal"], "gathered head slices differ from the single-rank result"
