@@ -158,7 +158,8 @@ class Workload:
     def launches_per_step(self):
         # per layer: the single decode kernel, which also appends the step's key/value rows (RI_WAVE_STAGED=1:
         # steady append, scan, select, attend), plus the flag wait of the peer-store gather
-        staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")
+        # geometries beyond 8192 centroids are outside the single kernel's range: the library runs the stages
+        staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0") or self.cfg.n_centroids > 8192
         return ((4 if staged else 1) + (1 if self.peer is not None else 0)) * self.geo.layers
 
     def static_len(self):
@@ -447,7 +448,8 @@ def run_decode(geo, args, rank, world, local_rank, log):
         return
     peak, _, peak_kind = measured_peaks()
     alg = algorithmic_bytes(wl, n_ret_rows, static_len)
-    staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0")   # the library's switch to the three-kernel form
+    # the library's switch to the three-kernel form, which it also takes beyond 8192 centroids
+    staged = os.environ.get("RI_WAVE_STAGED", "0") not in ("", "0") or wl.cfg.n_centroids > 8192
     alg["decode"] = sum(alg.values())                # the single kernel does all three stages' work
     kernels = {n: {"ms": round(stage_ms[n], 5), "alg_bytes": int(alg[n]), "gbs": round(alg[n] / stage_ms[n] / 1e6, 1),
                    "frac": round(alg[n] / stage_ms[n] / 1e6 / peak, 4)} for n in stage_ms}
