@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Decode-throughput benchmark of the wave-index attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config cfg1|cfg2] [--with-model]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config cfg1|cfg2|cfg3|cfg4] [--no-model]
 
 Workload (default, N=1): Llama-3-8B decode-attention geometry — 32 layers, 32 q / 8 kv heads,
 head_dim 128, batch 4, context 131072, 8192 centroids per kv head, budget 0.018, estimate 0.232 —
@@ -11,10 +11,14 @@ layer ``decode_update_kv_cache`` + ``compute``.
 
 Prints ONE JSON line (rank 0).  ``value`` is tokens/s with every input resident in HBM and the
 whole step replayed as one CUDA graph; ``e2e`` is the same step with q/k/v starting in pinned host
-memory and the attention output copied back to the host inside the timed region.
+memory and the attention output copied back to the host inside the timed region.  On one GPU the line
+also carries ``parity`` (layer 0 of the workload on the GPU against the CPU oracle: selected sets with the
+1e-3 tie rule, kept clusters, attention error), ``decode_model`` (the whole model step — projections, MLP,
+vocabulary head with random weights — around the same caches; ``--no-model`` skips it) and ``kmeans``
+(the prefill clustering of configuration 2 against the tensor-core roofline).
 
 ``--config cfg2`` times the prefill clustering alone (32 groups x 131072 keys, 8192 centroids,
-10 iterations) against the tensor-core roofline.
+10 iterations) in more detail.
 """
 from __future__ import annotations
 
@@ -39,7 +43,8 @@ from retrievalattention_b200.synthetic import make_kv  # noqa: E402
 SINK, RECENT = 4, 64
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
-NCU_TRAFFIC_DECODE = 118.4e6   # dram__bytes_read.sum + dram__bytes_write.sum per launch of wave_fused_kernel (profiles/wave_fused_cfg1_2layers.md)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from ncu captures of one layer of configuration 1 (32 groups)
+NCU_TRAFFIC = {"decode": 118.4e6, "scan": 70.18e6, "select": 6.33e6, "attend": 46.67e6}
 METRIC = "decode tok/s at 128K ctx (Llama-3-8B geometry); attn kernel HBM GB/s vs peak"
 
 
@@ -170,6 +175,7 @@ class Workload:
 # measurement helpers
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
+    PERIOD_MS = 20
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -180,7 +186,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu_index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.gpu_index), "-lms", str(self.PERIOD_MS)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -268,8 +274,9 @@ def time_stages(wl, first_step, steps):
     return ms, n_ret / len(layers), wl.static_len()
 
 
-def cpu_layer_seconds(wl, layer_idx, step, repeats):
-    """The oracle port of the reference arithmetic for one layer (all groups) on the host cores."""
+def cpu_layer_seconds(wl, layer_idx, step, repeats, static_len=SINK + RECENT + 1, with_parts=False):
+    """The oracle port of the reference arithmetic for one layer (all groups) on the host cores.
+    Returns the median seconds per evaluation (and, on request, the output and the selection it made)."""
     from oracle import attention as oat
 
     torch.set_num_threads(os.cpu_count())
@@ -285,15 +292,48 @@ def cpu_layer_seconds(wl, layer_idx, step, repeats):
     times = []
     for _ in range(repeats + 1):
         t0 = time.perf_counter()
-        oat.compute(q, cpu["centroids"], cpu["value_sum"], cpu["size"], cpu["count"] == 0, cpu["count"], cpu["offset"],
-                    cpu["keys"], cpu["values"], cpu["sk"], cpu["sv"], SINK + RECENT + 1, s.nprobe,
-                    s.nprobe + s.n_estimate, s.page_size, s.buffer_pages)
+        ref, parts = oat.compute(q, cpu["centroids"], cpu["value_sum"], cpu["size"], cpu["count"] == 0, cpu["count"],
+                                 cpu["offset"], cpu["keys"], cpu["values"], cpu["sk"], cpu["sv"], static_len, s.nprobe,
+                                 s.nprobe + s.n_estimate, s.page_size, s.buffer_pages, return_parts=True)
         times.append(time.perf_counter() - t0)
-    return statistics.median(times[1:])
+    sec = statistics.median(times[1:])
+    return (sec, ref, parts) if with_parts else sec
+
+
+def layer_parity(wl, layer_idx, step):
+    """Layer ``layer_idx`` of the workload, all groups, one decode step: the GPU path (through the C ABI, with the
+    id outputs switched on) against the CPU oracle fed the same index, query and steady zone.  Also returns the
+    oracle's seconds per evaluation, which is the CPU baseline's sample."""
+    from oracle import score_select as oss
+    from retrievalattention_b200 import wave
+
+    bound = wl.cache._layers[layer_idx]
+    s = wl.shape
+    static_len = wl.static_len()
+    t = dict(bound.t)
+    t["scratch"] = wave.new_scratch(s, wl.device)
+    probe = wave.WaveIndexLayer(s, want_ids=True, **t)
+    q = wl.q_all[step, layer_idx].contiguous()
+    out = probe.compute(q)
+    torch.cuda.synchronize()
+    sec, ref, parts = cpu_layer_seconds(wl, layer_idx, step, 2, static_len=static_len, with_parts=True)
+    ret, est = probe.retrieved_ids.cpu(), probe.estimated_ids.cpu()
+    err = (out.cpu().float() - ref.float()).abs()
+    parity = {
+        "config": f"layer {layer_idx} of the workload, all {s.groups} groups, GPU (C ABI, id outputs on) vs CPU oracle",
+        "max_abs": round(float(err.max()), 5), "mean_abs": round(float(err.mean()), 6),
+        "tolerance": "max_abs <= 2e-2, mean_abs <= 2e-3; sets bit-exact outside a 1e-3 tie band at the cut",
+        "retrieval_sets_ok": bool(oss.selection_matches(parts["dist"], ret, s.nprobe)),
+        "estimation_sets_ok": bool(oss.selection_matches(parts["dist"], torch.cat((ret, est), 1), s.nprobe + s.n_estimate)),
+        "kept_ok": probe.retrieved_kept.cpu().tolist() == list(parts["kept"]),
+    }
+    parity["ok"] = bool(parity["retrieval_sets_ok"] and parity["estimation_sets_ok"] and parity["kept_ok"]
+                        and parity["max_abs"] <= 2e-2 and parity["mean_abs"] <= 2e-3)
+    return parity, sec
 
 
 def model_decode(wl, geo, args, warm, log):
-    """Decode tokens/s of the whole model step around the same caches (``--with-model``): embedding,
+    """Decode tokens/s of the whole model step around the same caches: embedding,
     per layer RMS norm -> fused QKV projection -> rotary embedding -> cache update + wave-index
     attention -> output projection -> RMS norm -> MLP, final norm, vocabulary projection and greedy
     arg-max, with seeded random weights at the model's published shapes; one CUDA graph per step.
@@ -363,14 +403,15 @@ def run_decode(geo, args, rank, world, local_rank, log):
             os.environ["NCCL_DEBUG"] = "ERROR"     # keep NCCL's banner off stdout: one JSON line only
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-        # Host-side barriers and the max-over-ranks reduction go over gloo: an eager NCCL collective
-        # issued after graph-captured ones on the same communicator did not return on this pool.
+        # Host-side barriers and the max-over-ranks reduction go over gloo, so that no eager NCCL collective
+        # is ever issued on a communicator that also carries graph-captured work.
         cpu_group = dist.new_group(backend="gloo")
 
     warm = max(args.warmup, 3)
     stage_steps = min(args.steps, 4)
     total = 2 * (warm + args.steps) + stage_steps + 2
-    if args.with_model:
+    with_model = world == 1 and not args.no_model
+    if with_model:
         total += 2 * (warm + args.steps) + 2      # the model run appends to the same steady zones
     wl = Workload(geo, device, total, args.kmeans_iters, rank, log, world)
     wl.capture()      # consumes 2 steps of the steady zone
@@ -388,7 +429,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
     # ---- `value`: inputs resident in HBM, one graph replay per step ----
     run_resident(0, warm)
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank)     # samples over both timed regions (value and e2e)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -397,7 +438,6 @@ def run_decode(geo, args, rank, world, local_rank, log):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- `e2e`: q/k/v start in pinned host memory, outputs end there ----
     base = warm + args.steps
@@ -420,6 +460,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
 
     gather_check = None
     if world > 1:
@@ -455,12 +496,10 @@ def run_decode(geo, args, rank, world, local_rank, log):
                    "frac": round(alg[n] / stage_ms[n] / 1e6 / peak, 4)} for n in stage_ms}
     top = max(("scan", "select", "attend"), key=stage_ms.get) if staged else "decode"
     kernel_name = {"decode": "wave_fused_kernel"}.get(top, "wave_" + top + "_kernel")
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-    # profiles/ (one layer of this workload's geometry, 32 groups); scaled by the groups of this rank.
-    ncu_traffic = {"decode": NCU_TRAFFIC_DECODE, "scan": 70.18e6, "select": 6.33e6, "attend": 46.67e6}
+    # measured DRAM traffic of one launch (ncu capture of this geometry with 32 groups), scaled by this rank's groups
     traffic = None
-    if geo.name.startswith("llama3-8b-128k") and ncu_traffic[top]:
-        traffic = int(ncu_traffic[top] * wl.shape.groups / 32)
+    if geo.name.startswith("llama3-8b-128k") and NCU_TRAFFIC[top]:
+        traffic = int(NCU_TRAFFIC[top] * wl.shape.groups / 32)
     step_alg = alg["decode"] * geo.layers
     tokens = geo.batch * world * args.steps
     cfg = wl.cfg
@@ -500,18 +539,33 @@ def run_decode(geo, args, rank, world, local_rank, log):
                      "path": {"alg_bytes_per_step": int(step_alg), "gbs": round(step_alg / (ms / args.steps) / 1e6, 1),
                               "frac": round(step_alg / (ms / args.steps) / 1e6 / peak, 4)}},
     }
-    if args.with_model and world == 1:
-        result["decode_model"] = model_decode(wl, geo, args, warm, log)
-        mb = result["decode_model"].get("weight_bytes_per_step")
+    cfgd = result["config"]
+    cfgd["kernels"] = "; ".join(f"{n} {k['ms'] * 1e3:.1f}us {k['gbs']:.0f}GB/s {k['frac']:.3f}" for n, k in kernels.items())
+    if with_model:
+        dm = result["decode_model"] = model_decode(wl, geo, args, warm, log)
+        mb = dm.get("weight_bytes_per_step")
         if mb:
-            gbs = (mb + step_alg) / result["decode_model"]["ms_per_step"] / 1e6
-            result["decode_model"].update({"gbs": round(gbs, 1), "frac": round(gbs / peak, 4)})
+            gbs = (mb + step_alg) / dm["ms_per_step"] / 1e6
+            dm.update({"gbs": round(gbs, 1), "frac": round(gbs / peak, 4)})
+            cfgd["decode_model"] = (f"whole model step: {dm['tok_s']} tok/s ({dm['ms_per_step']} ms/step), {dm['e2e_tok_s']} tok/s "
+                                    f"with host token ids, {gbs:.0f} GB/s = {gbs / peak:.3f} of peak")
+        else:
+            cfgd["decode_model"] = dm.get("unavailable", "unavailable")
     if not args.no_cpu_baseline:
-        sec = cpu_layer_seconds(wl, 0, warm, 2)
+        parity, sec = layer_parity(wl, 0, warm)
+        result["parity"] = parity
+        cfgd["parity"] = (f"layer 0, {geo.groups} groups vs CPU oracle: " + ("ok" if parity["ok"] else "FAILED")
+                          + f", max_abs {parity['max_abs']}, mean_abs {parity['mean_abs']}, sets "
+                          + f"{parity['retrieval_sets_ok']}/{parity['estimation_sets_ok']}, kept {parity['kept_ok']}")
         result["cpu_baseline"] = {"value": round(geo.batch / (sec * geo.layers), 3), "unit": "tok/s",
                                   "cores": os.cpu_count(), "kind": "port",
                                   "sample": f"layer 0 of the same workload, all {geo.groups} groups, median of 2 runs "
                                             f"({sec * 1e3:.1f} ms), scaled by {geo.layers} layers"}
+    if world == 1 and not args.no_kmeans and args.config == "cfg1":
+        km = kmeans_summary(GEOMETRIES["cfg2"], args, log)
+        result["kmeans"] = km
+        cfgd["kmeans"] = (f"cfg2 build {km['ms']} ms, {km['tflops']} TFLOP/s = {km['frac']} of sustained bf16 peak "
+                          f"({km['frac_of_burst_peak']} of burst)")
     print(json.dumps(result), flush=True)
     if world > 1:
         dist.barrier(group=cpu_group)
@@ -543,18 +597,61 @@ def reference_arm(geo, args, log):
 # ----------------------------------------------------------------------------------------------
 # clustering benchmark (config 2)
 # ----------------------------------------------------------------------------------------------
+def kmeans_inputs(geo, device):
+    ks, vs = [], []
+    for b in range(geo.batch):
+        k, v = make_kv(geo.kv_heads, geo.context, 128, seed=b, theta=geo.rope_theta, device=device)
+        ks.append(k[0].transpose(0, 1)); vs.append(v[0].transpose(0, 1))
+    return torch.cat(ks, 0).contiguous(), torch.cat(vs, 0).contiguous()
+
+
+def sustained_and_burst_tflops():
+    _, burst, kind = measured_peaks()
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            sustained = json.load(f).get("bf16_tflops_sustained")
+        if sustained:
+            return float(sustained), burst, kind + " (sustained)"
+    return burst, burst, kind
+
+
+def kmeans_summary(geo, args, log):
+    """Configuration 2 in short, for the default line: one warm build, three timed (reference schedule)."""
+    from retrievalattention_b200.cache_hub.kmeans import build_index
+
+    device = torch.device("cuda", 0)
+    cfg = geo.index()
+    keys, values = kmeans_inputs(geo, device)
+    r = build_index(keys, values, cfg.n_centroids, cfg.n_segment, args.kmeans_iters)
+    torch.cuda.synchronize()
+    assert int(r["error"]) == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        r = build_index(keys, values, cfg.n_centroids, cfg.n_segment, args.kmeans_iters)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    it = args.kmeans_iters
+    flop = 2.0 * geo.groups * geo.context * 128 * (cfg.n_centroids * (it - 1) / cfg.n_segment + cfg.n_centroids)
+    sustained, burst, kind = sustained_and_burst_tflops()
+    tf = flop / ms / 1e9
+    log(f"k-means (cfg2): {ms:.2f} ms, {tf:.1f} TFLOP/s")
+    return {"workload": f"ri_kmeans_build: {geo.groups} groups x {geo.context} keys x d128, {cfg.n_centroids} centroids, "
+                        f"{cfg.n_segment} segments, {it} iterations, incl. centring, value sums and layout",
+            "ms": round(ms, 3), "tflops": round(tf, 1), "bound": "tensor", "peak": sustained, "peak_kind": "of " + kind,
+            "frac": round(tf / sustained, 4), "frac_of_burst_peak": round(tf / burst, 4)}
+
+
 def run_kmeans(geo, args, log):
     from retrievalattention_b200.cache_hub.kmeans import build_index
 
     device = torch.device("cuda", 0)
     cfg = geo.index()
     n = geo.context
-    ks, vs = [], []
-    for b in range(geo.batch):
-        k, v = make_kv(geo.kv_heads, n, 128, seed=b, theta=geo.rope_theta, device=device)
-        ks.append(k[0].transpose(0, 1)); vs.append(v[0].transpose(0, 1))
-    keys, values = torch.cat(ks, 0).contiguous(), torch.cat(vs, 0).contiguous()
-    del ks, vs
+    keys, values = kmeans_inputs(geo, device)
     results = {}
     schedules = (("reference schedule", cfg.n_segment),) if args.quick else \
         (("reference schedule", cfg.n_segment), ("plain Lloyd", 1))
@@ -578,16 +675,8 @@ def run_kmeans(geo, args, log):
         flop = 2.0 * g * n * 128 * (c * (it - 1) / segs + c)
         results[label] = {"segments": segs, "ms": round(ms, 3), "tflops": round(flop / ms / 1e9, 1), "flop": flop}
         log(f"{label}: {ms:.2f} ms, {flop / ms / 1e9:.1f} TFLOP/s")
-    _, peak_tf, kind = measured_peaks()
     # builds run back to back for tens of milliseconds: the sustained matmul figure is the denominator
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    sustained = None
-    if os.path.exists(path):
-        with open(path) as f:
-            sustained = json.load(f).get("bf16_tflops_sustained")
-    burst_tf = peak_tf
-    if sustained:
-        peak_tf, kind = float(sustained), kind + " (sustained)"
+    peak_tf, burst_tf, kind = sustained_and_burst_tflops()
     main = results["reference schedule"]
     print(json.dumps({
         "metric": "prefill k-means clustering time (config 2)", "value": main["ms"], "unit": "ms", "n_gpus": 1,
@@ -599,8 +688,7 @@ def run_kmeans(geo, args, log):
         "roofline": {"bound": "tensor", "achieved": main["tflops"], "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": round(main["tflops"] / peak_tf, 4), "peak_kind": "of " + kind,
                      "frac_of_burst_peak": round(main["tflops"] / burst_tf, 4),
-                     "note": "whole build (centring, assignment, bucket, update, layout) over the assignment GEMM's flops; "
-                             "the assignment kernel alone keeps the tensor pipe 67 % active (profiles/)",
+                     "note": "whole build (centring, assignment, bucket, update, layout) over the assignment GEMM's flops",
                      "traffic": None, "schedules": results},
     }), flush=True)
 
@@ -615,9 +703,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override layer count (profiling on a small case only)")
     ap.add_argument("--kmeans-iters", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--with-model", action="store_true",
-                    help="also time the whole model decode step (projections, MLP, vocabulary head with random weights) "
-                         "around the same caches; adds the key decode_model (single GPU)")
+    ap.add_argument("--no-model", action="store_true",
+                    help="skip the whole-model decode step (projections, MLP, vocabulary head with random weights around "
+                         "the same caches; key decode_model, single GPU)")
+    ap.add_argument("--no-kmeans", action="store_true", help="skip the short clustering run (key kmeans, single GPU)")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
     args = ap.parse_args()
 
@@ -639,8 +728,8 @@ def main():
         return
     run_decode(geo, args, rank, world, local_rank, log)
     if world > 1:
-        # leave without tearing the NCCL communicator down (its teardown after graph-captured
-        # collectives did not return on this pool); everything has been printed and flushed
+        # leave without tearing the NCCL communicator down (a teardown after graph-captured collectives
+        # has been seen not to return); everything has been printed and flushed
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)

@@ -147,8 +147,9 @@ typedef struct ri_wave_gather {
   const uint32_t* d_epoch;         /* local: [1] the current step's epoch */
   int32_t* d_error;                /* local: set to 1 when a wait ran out */
 } ri_wave_gather;
-/* ri_wave_decode_layer plus the stores described above (p->d_out is written too).
- * RI_ERR_INVALID for geometries the single decode kernel does not cover (more than 8192 centroids). */
+/* ri_wave_decode_layer plus the stores described above (p->d_out is written too).  Geometries beyond the single
+ * decode kernel (more than 8192 centroids, e.g. after a re-index of generated tokens) run the three stage
+ * kernels, whose attend stage does the stores. */
 int ri_wave_decode_layer_gather(const ri_wave_layer* p, const ri_wave_gather* g, void* stream);
 /* Raise this rank's flags, then wait (bounded) for every rank's. */
 int ri_wave_gather_wait(const ri_wave_gather* g, void* stream);
@@ -161,6 +162,9 @@ typedef struct ri_wave_views {
   const int32_t* d_n_exact;     /* [G] retrieved rows (without the steady zone) */
 } ri_wave_views;
 int ri_wave_scratch_views(const ri_wave_layer* p, ri_wave_views* out);
+/* Test hook: limit the estimation entries a CTA of the single decode kernel keeps in shared memory (0 forces its
+ * global lists, a small value the mixed case); negative restores the default.  Process-wide. */
+int ri_wave_test_local_cap(int cap);
 
 /* Append this step's key/value to the steady zone at row *d_position.
  * Replaces cache_hub/retroinfer_cache.py:538-540 (`decode_update_kv_cache`).

@@ -24,6 +24,11 @@ OUT_DIR = os.path.join(HERE, "_ref")
 SRC_REL = "library/retroinfer/retroinfer_kernels/src/wave_buffer_cpu.cpp"
 
 
+def default_reference_root() -> str:
+    """``RI_REFERENCE_ROOT`` if set, else a checkout named ``reference`` beside this repository."""
+    return os.environ.get("RI_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def module_path() -> str:
     return os.path.join(OUT_DIR, "WaveBuffer" + sysconfig.get_config_var("EXT_SUFFIX"))
 
@@ -31,9 +36,9 @@ def module_path() -> str:
 def build(reference_root: str | None = None, force: bool = False) -> str | None:
     """Returns the path of the built module, or None when the reference checkout is
     not present (then a previously built module, if any, keeps being used)."""
-    reference_root = reference_root or os.environ.get("RI_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
-    src = os.path.join(reference_root, SRC_REL)
+    reference_root = reference_root or default_reference_root()
     out = module_path()
+    src = os.path.join(reference_root, SRC_REL)
     if not os.path.exists(src):
         return out if os.path.exists(out) else None
     if os.path.exists(out) and not force and os.path.getmtime(out) >= os.path.getmtime(src):

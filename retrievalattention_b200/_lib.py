@@ -11,7 +11,8 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libri_b200.so")
+# RI_B200_LIB names another build of the same library (e.g. one installed outside the package)
+LIB_PATH = os.environ.get("RI_B200_LIB") or os.path.join(_PKG, "lib", "libri_b200.so")
 
 RI_BF16, RI_F16 = 0, 1
 
@@ -76,6 +77,8 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]
+    lib.ri_wave_test_local_cap.restype = C.c_int
+    lib.ri_wave_test_local_cap.argtypes = [C.c_int]
     lib.ri_wave_attend_buffer.restype = C.c_int
     lib.ri_wave_attend_buffer.argtypes = [C.POINTER(WaveLayer), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.ri_wave_decode_layer_gather.restype = C.c_int

@@ -23,7 +23,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libri_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", f"-I{INCLUDE}", f"-I{CSRC}"]
-NVCC_FLAGS += shlex.split(os.environ.get("RI_NVCC_EXTRA", ""))   # e.g. -DRI_FUSED_TRACE for a timing build
+NVCC_FLAGS += shlex.split(os.environ.get("RI_NVCC_EXTRA", ""))   # extra compiler flags (e.g. -Xptxas=-v)
 
 
 def _sources():

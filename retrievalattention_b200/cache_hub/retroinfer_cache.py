@@ -131,6 +131,9 @@ class retroinfer_cache(KV_Cache):
         from ..kernels import ThreadPool, WaveBufferCPU
 
         g, d = self.batch_groups, self.head_dim
+        if self.page_size != 8:
+            raise ValueError("the host tier's copy kernels move pages of 8 rows (as the reference's, gather_copy.cu:11): "
+                             f"cache_unit_size must be 8, got {self.page_size}")
         self.cache_size = max(self.cache_size, 1)
         self.execution_stride = self.buffer_size * self.page_size + self.static_stride
         self.thread_pool = ThreadPool(self.core)
@@ -249,8 +252,10 @@ class retroinfer_cache(KV_Cache):
             dev = self.layer_mapping[str(ldx)]
             with torch.cuda.device(dev):
                 sk, sv = self.steady_zone_keys[ldx], self.steady_zone_values[ldx]
-                update_keys = sk[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).contiguous()
-                update_values = sv[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).contiguous()
+                # copies, not views (:465-466): with one group the slice is already contiguous and the window move
+                # below would overwrite its first rows before the clustering reads them
+                update_keys = sk[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).clone()
+                update_values = sv[:, :, start:total - end].reshape(g, THRESHOLD_LENGTH, d).clone()
                 tail_k, tail_v = sk[:, :, total - end:total].clone(), sv[:, :, total - end:total].clone()
                 sk[:, :, start:start + end] = tail_k        # move the local window (:469-472)
                 sv[:, :, start:start + end] = tail_v

@@ -29,9 +29,13 @@ int attend_ctas() {
 }
 
 template <int DT>
-int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb) {
+int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb, const ri_wave_gather* gather) {
   AttendArgs a;
   fill_attend_args(p, L, eb, a);
+  if (gather) {
+    a.copies = reinterpret_cast<uint16_t* const*>(gather->d_out_slots);
+    a.n_copies = gather->n_ranks;
+  }
   const int clusters = min(p.groups, max(1, attend_ctas() / kAttendCluster));
   const int ctas = clusters * kAttendCluster;
   RI_CUDA_OK(cudaFuncSetAttribute(wave_attend_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes));
@@ -72,8 +76,9 @@ int launch_weighted_decoding(const void* q, const void* k, const void* v, const 
   return dtype == RI_BF16 ? launch_operator<RI_BF16>(a, s) : launch_operator<RI_F16>(a, s);
 }
 
-int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb) {
-  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s, eb) : launch<RI_F16>(p, L, s, eb);
+int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb,
+                  const ri_wave_gather* gather) {
+  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s, eb, gather) : launch<RI_F16>(p, L, s, eb, gather);
 }
 
 }  // namespace ri_wave

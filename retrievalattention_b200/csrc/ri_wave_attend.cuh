@@ -117,27 +117,38 @@ struct LocalLists {
   int x_lo, x_hi;            // this CTA's exact steps [x_lo, x_hi) of ceil((steady + n_rows) / 16)
 };
 
-// One group's attention by one 8-CTA cluster (CTA `cl` of it).  `ring`: kRingBytes of 16-byte aligned
-// dynamic shared memory.  `n_exact_known` >= 0: the group's retrieved-row count, when the caller has it at
+// The value-sum rows of one estimation step (pieces 8..15 of a ring stage), ids = this lane's four clusters.
+__device__ __forceinline__ void issue_value_sums(const uint4* value_sum, int64_t g, int C, uint32_t dst, const int (&ids)[4], int r) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4* p = value_sum + (g * C + ids[i]) * 16;
+    cp_async16(dst + (8 + 2 * i) * 512, p + r);
+    cp_async16(dst + (9 + 2 * i) * 512, p + r + 8);
+  }
+}
+
+// One group's attention by one cluster of CPG CTAs of WARPS warps each (CTA `cl` of it).  `ring`:
+// WARPS * kStages * kStageBytes of 16-byte aligned dynamic shared memory.  `n_exact_known` >= 0: the group's retrieved-row count, when the caller has it at
 // hand (otherwise it is read from a.n_exact).  Ends with a cluster barrier after the last remote read, so the shared
 // memory may be reused (or the CTA may exit) when it returns.
-template <int DT, bool LOCAL = false>
+template <int DT, bool LOCAL = false, int WARPS = 4, int CPG = kAttendCluster>
 __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, const int cl, uint8_t* ring,
                                              const LocalLists* ll = nullptr) {
-  __shared__ float sm_m[4][kMaxHeads], sm_l[4][kMaxHeads];
+  __shared__ float sm_m[WARPS][kMaxHeads], sm_l[WARPS][kMaxHeads];
   __shared__ float cta_m[kMaxHeads], cta_l[kMaxHeads];   // this CTA's partial result: (max, sum) here, O in the ring
-  float (*cta_o)[RI_HEAD_DIM] = reinterpret_cast<float (*)[RI_HEAD_DIM]>(ring + 4 * kStageBytes);
+  float (*cta_o)[RI_HEAD_DIM] = reinterpret_cast<float (*)[RI_HEAD_DIM]>(ring + WARPS * kStageBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
   const int gs = a.gs, es = LOCAL ? (ll->n_est + 15) / 16 : a.e_steps;
   const int static_len = a.static_len ? *a.static_len : 0;   // null: the exact rows already contain the steady zone
   cg::cluster_group cluster = cg::this_cluster();
-  constexpr int cpg = kAttendCluster;                    // CTAs per group
-  // ring: stage-major, slot (stage, warp) at (stage * 4 + warp) * kStageBytes
+  constexpr int cpg = CPG;                               // CTAs per group
+  constexpr int kThreads = WARPS * 32;
+  // ring: stage-major, slot (stage, warp) at (stage * WARPS + warp) * kStageBytes
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStageBytes + lane * 16;
   const uint8_t* my_ring_ptr = ring + warp * kStageBytes + lane * 16;
-  constexpr int kStageStride = 4 * kStageBytes;
+  constexpr int kStageStride = WARPS * kStageBytes;
   auto warp_o = [&](int w) { return reinterpret_cast<float*>(ring + w * kStageBytes); };   // stage 0 of warp w
 
   const int te = static_len + (LOCAL ? ll->n_rows : __ldcg(a.n_exact + g));           // steady + retrieved rows
@@ -150,20 +161,35 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
   // its first unit (an estimation step moves half the bytes but costs about two thirds of the time, measured)
   const int kCostEst = a.cost_est, kCostExact = a.cost_exact;
   const int units = kCostEst * es + kCostExact * xs;
-  const int n_w = LOCAL ? 4 : cpg * 4, wl = LOCAL ? warp : cl * 4 + warp;
+  const int n_w = LOCAL ? WARPS : cpg * WARPS, wl = LOCAL ? warp : cl * WARPS + warp;
   const int per = max(kCostExact, (units + n_w - 1) / n_w);
   auto steps_before_unit = [&](int u) {
     return u < kCostEst * es ? (u + kCostEst - 1) / kCostEst : es + (u - kCostEst * es + kCostExact - 1) / kCostExact;
   };
   const int lu = min(units, wl * per), hu = min(units, lu + per);
   const int lo = steps_before_unit(lu), hi = steps_before_unit(hu);
+  // This warp's steps, numbered j = 0 .. n_steps - 1.  Shared sequence (not LOCAL): steps lo .. hi - 1 of it.
+  // LOCAL: the CTA's estimation steps go round the warps (warp w: steps w, w + WARPS, ...), then a contiguous range
+  // of the CTA's exact steps, sized so that every warp ends up with the same number of steps (+-1).
+  int n_steps = hi - lo, e_w = 0, xa = 0;
+  if (LOCAL) {
+    const int S = es + xs;
+    e_w = es / WARPS + (warp < es % WARPS ? 1 : 0);
+    n_steps = S / WARPS + (warp < S % WARPS ? 1 : 0);
+    xa = x_first + (warp * (S / WARPS) + min(warp, S % WARPS)) - (warp * (es / WARPS) + min(warp, es % WARPS));
+  }
+  auto locate = [&](int j, bool& est, int& base) {
+    if (LOCAL) { est = j < e_w; base = (est ? warp + j * WARPS : xa + j - e_w) * 16; }
+    else { const int s = lo + j; est = s < es; base = (est ? s : s - es) * 16; }
+  };
 
-  // ids of the rows this lane touches in step s (called by whole warps, in increasing s)
+  // ids of the rows this lane touches in step j (called by whole warps, in increasing j)
   int hint = -1;               // LOCAL: kept cluster holding the first retrieved row of the step being resolved
-  auto load_ids = [&](int s) {
+  auto load_ids = [&](int j) {
     RowIds id;
-    const bool est = s < es;
-    const int base = (est ? s : x_first + s - es) * 16;
+    bool est;
+    int base;
+    locate(j, est, base);
     const int last = (est ? n_est_rows : te) - 1;
     const int tt[4] = {2 * t, 2 * t + 1, 8 + 2 * t, 9 + 2 * t};
     if (LOCAL && !est) {
@@ -205,14 +231,17 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
     }
     return id;
   };
-  // start the copies of step s into ring stage `stage`
-  auto issue = [&](int s, int stage, const RowIds& id) {
+  // start the copies of step j into ring stage `stage`
+  auto issue = [&](int j, int stage, const RowIds& id) {
     const uint32_t dst = my_ring + stage * kStageStride;
-    if (s < es) {
+    bool est;
+    int base;
+    locate(j, est, base);
+    if (est) {
       // pieces 0/1: this lane's scores and weights of the step (LOCAL: read from the lists when the step
       // is consumed); pieces 8..15: value-sum rows
       if (!LOCAL) {
-        const int i0 = s * 16 + 2 * t;
+        const int i0 = base + 2 * t;
         if (r < gs) {
           const float* sp = a.est_s2 + ((int64_t)g * kMaxHeads + r) * a.e_pad + i0;
           cp_async8(dst, sp);
@@ -222,12 +251,7 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
         cp_async8(dst + 512, wp);
         cp_async8(dst + 512 + 8, wp + 8);
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4* p = a.value_sum + ((int64_t)g * a.C + id.v[i]) * 16;
-        cp_async16(dst + (8 + 2 * i) * 512, p + r);
-        cp_async16(dst + (9 + 2 * i) * 512, p + r + 8);
-      }
+      issue_value_sums(a.value_sum, g, a.C, dst, id.v, r);
     } else {
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
@@ -250,19 +274,19 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
 
   // ---- prologue: fill the ring (the ids of all its steps are fetched before the first copy is issued,
   //      so their latencies overlap) ----
-  int s_issue = lo;
+  int j_issue = min(kStages, n_steps);
   RowIds nid;
   {
     RowIds pid[kStages];
 #pragma unroll
     for (int st = 0; st < kStages; ++st)
-      if (lo + st < hi) pid[st] = load_ids(lo + st);
+      if (st < n_steps) pid[st] = load_ids(st);
 #pragma unroll
     for (int st = 0; st < kStages; ++st) {
-      if (s_issue < hi) { issue(s_issue, st, pid[st]); ++s_issue; }
+      if (st < n_steps) issue(st, st, pid[st]);
       cp_async_commit();
     }
-    if (s_issue < hi) nid = load_ids(s_issue);
+    if (j_issue < n_steps) nid = load_ids(j_issue);
   }
   uint4 qa[4];
 #pragma unroll
@@ -276,10 +300,13 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
   float m_run = -INFINITY, l_run = 0.f;   // head r (l: this lane's share, reduced over the quad at the end)
   int stage = 0;
 #pragma unroll 1
-  for (int s = lo; s < hi; ++s) {
+  for (int j = 0; j < n_steps; ++j) {
+    bool is_est;
+    int base;
+    locate(j, is_est, base);
     float rw[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
-    if (!LOCAL && a.row_w != nullptr && s >= es) {   // operator form: weights of this lane's four exact rows
-      const int b0 = (x_first + s - es) * 16 + 2 * t;
+    if (!LOCAL && a.row_w != nullptr && !is_est) {   // operator form: weights of this lane's four exact rows
+      const int b0 = base + 2 * t;
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
@@ -289,10 +316,8 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
         }
     }
     cp_async_wait<kStages - 1>();           // the group of step s has landed (lane-private slots: no barrier)
-    if (s == lo) RI_FT(10);
+    if (j == 0) RI_FT(10);
     const uint8_t* src = my_ring_ptr + stage * kStageStride;
-    const bool is_est = s < es;
-    const int base = (is_est ? s : x_first + s - es) * 16;
     const int rows_end = is_est ? n_est_rows : te;
 
     float s2[2][2];
@@ -300,7 +325,7 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
     if (is_est) {
       float4 sv, wv;
       if (LOCAL) {
-        const int j0 = s * 16 + 2 * t;               // < cap: cap is a multiple of 16 and n_est <= cap
+        const int j0 = base + 2 * t;                 // < cap: cap is a multiple of 16 and n_est <= cap
         const float2 a0 = *reinterpret_cast<const float2*>(ll->est_sc + (r < gs ? r : 0) * ll->cap + j0);
         const float2 a1 = *reinterpret_cast<const float2*>(ll->est_sc + (r < gs ? r : 0) * ll->cap + j0 + 8);
         const float2 w0 = *reinterpret_cast<const float2*>(ll->est_wt + j0);
@@ -370,10 +395,10 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
     pv_step<DT>(acc, v, Elem<DT>::pack2(p[0][0], p[0][1]), Elem<DT>::pack2(p[1][0], p[1][1]));
 
     // refill the stage just consumed (the same lane wrote and read it), then fetch the ids after that
-    if (s_issue < hi) {
-      issue(s_issue, stage, nid);
-      ++s_issue;
-      if (s_issue < hi) nid = load_ids(s_issue);
+    if (j_issue < n_steps) {
+      issue(j_issue, stage, nid);
+      ++j_issue;
+      if (j_issue < n_steps) nid = load_ids(j_issue);
     }
     cp_async_commit();
     stage = stage + 1 == kStages ? 0 : stage + 1;
@@ -381,7 +406,7 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
   cp_async_wait<0>();
   RI_FT(11);
 
-  // ---- merge the four warps of this CTA (each parks its 8 x 128 accumulator in its own idle ring region) ----
+  // ---- merge the warps of this CTA (each parks its 8 x 128 accumulator in its own idle ring region) ----
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
   if (t == 0) { sm_m[warp][r] = m_run; sm_l[warp][r] = l_run; }
@@ -397,26 +422,30 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
     }
   }
   __syncthreads();
-  for (int h = 0; h < gs; ++h) {
-    const float M = fmaxf(fmaxf(sm_m[0][h], sm_m[1][h]), fmaxf(sm_m[2][h], sm_m[3][h]));
+  for (int idx = tid; idx < gs * RI_HEAD_DIM; idx += kThreads) {
+    const int h = idx >> 7, ch = idx & (RI_HEAD_DIM - 1);
+    float M = -INFINITY;
+#pragma unroll
+    for (int wi = 0; wi < WARPS; ++wi) M = fmaxf(M, sm_m[wi][h]);
     const float Ms = M == -INFINITY ? 0.f : M;
     float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
+    for (int wi = 0; wi < WARPS; ++wi) {
       const float f = exp2f(sm_m[wi][h] - Ms);
       L += sm_l[wi][h] * f;
-      O += warp_o(wi)[h * RI_HEAD_DIM + tid] * f;
+      O += warp_o(wi)[h * RI_HEAD_DIM + ch] * f;
     }
-    cta_o[h][tid] = O;
-    if (tid == 0) { cta_m[h] = M; cta_l[h] = L; }
+    cta_o[h][ch] = O;
+    if (ch == 0) { cta_m[h] = M; cta_l[h] = L; }
   }
   cluster.sync();
   RI_FT(12);
 
-  // ---- merge the 8 partial results of the group through distributed shared memory: this CTA
-  //      finishes values [cl * gs*16, (cl+1) * gs*16) of the gs*128 outputs ----
-  if (tid < gs * 16) {
-    const int v = cl * gs * 16 + tid, h = v >> 7, ch = v & 127;
+  // ---- merge the partial results of the group's CTAs through distributed shared memory: this CTA
+  //      finishes values [cl * share, (cl+1) * share) of the gs*128 outputs ----
+  const int share = gs * RI_HEAD_DIM / cpg;
+  for (int tv = tid; tv < share; tv += kThreads) {
+    const int v = cl * share + tv, h = v >> 7, ch = v & 127;
     float mc[cpg], lc[cpg], oc[cpg];
 #pragma unroll
     for (int c = 0; c < cpg; ++c) {

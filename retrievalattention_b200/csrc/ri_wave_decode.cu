@@ -105,14 +105,14 @@ extern "C" int ri_wave_attend_buffer(const ri_wave_layer* p, const void* d_exec_
   return launch_attend(*p, L, static_cast<cudaStream_t>(stream), &eb);
 }
 
-extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
-  int rc = validate(p);
-  if (rc != RI_OK) return rc;
+namespace {
+// One layer's decode step: the single kernel where it covers the geometry, else the three stage kernels.
+int decode_layer(const ri_wave_layer* p, const ri_wave_gather* gather, cudaStream_t s) {
+  int rc;
   const Layout L = make_layout(*p);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   // RI_WAVE_STAGED=1 keeps the three-kernel form (profiling one stage at a time, A/B timing)
   static const bool staged = getenv("RI_WAVE_STAGED") && atoi(getenv("RI_WAVE_STAGED")) != 0;
-  if (!staged && fused_supported(*p)) return launch_fused(*p, L, s);
+  if (!staged && fused_supported(*p)) return launch_fused(*p, L, s, gather);
   if (p->d_new_keys) {   // the three-kernel form appends with the stand-alone kernel (row *d_static_len - 1)
     const int n = p->groups * 16;
     RI_CUDA_OK(ri_launch_pdl_id(4, steady_append_kernel, dim3((n + 255) / 256), dim3(256), 0, s,
@@ -123,7 +123,14 @@ extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
   }
   if ((rc = launch_scan(*p, L, s)) != RI_OK) return rc;
   if ((rc = launch_select(*p, L, s)) != RI_OK) return rc;
-  return launch_attend(*p, L, s);
+  return launch_attend(*p, L, s, nullptr, gather);
+}
+}  // namespace
+
+extern "C" int ri_wave_decode_layer(const ri_wave_layer* p, void* stream) {
+  const int rc = validate(p);
+  if (rc != RI_OK) return rc;
+  return decode_layer(p, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 namespace {
@@ -140,9 +147,7 @@ extern "C" int ri_wave_decode_layer_gather(const ri_wave_layer* p, const ri_wave
   int rc = validate(p);
   if (rc != RI_OK) return rc;
   if ((rc = validate_gather(g)) != RI_OK) return rc;
-  RI_REQUIRE(fused_supported(*p), "the gather form needs the single decode kernel (n_centroids=%d too large)", p->n_centroids);
-  const Layout L = make_layout(*p);
-  return launch_fused(*p, L, static_cast<cudaStream_t>(stream), g);
+  return decode_layer(p, g, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ri_wave_gather_wait(const ri_wave_gather* g, void* stream) {

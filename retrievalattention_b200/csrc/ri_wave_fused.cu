@@ -1,4 +1,5 @@
-// The whole decode step of one layer in ONE kernel: an 8-CTA thread-block cluster per group runs
+// The whole decode step of one layer in ONE kernel: a thread-block cluster per group (CL = 4 or 8 CTAs of
+// 256 threads, one CTA per SM) runs
 //   phase 1  scan    s = alpha * q.C^T over the group's centroids (each CTA one slice, streamed
 //                    through the lane-private cp.async ring), per-CTA softmax partials exchanged
 //                    through distributed shared memory;
@@ -7,8 +8,11 @@
 //   phase 3  attend  the shared attention body (ri_wave_attend.cuh) over the group's estimation
 //                    and exact rows.
 // Groups are independent, so nothing crosses a cluster: the two kernel boundaries of the staged
-// path (drain, launch, ramp-up, and the scores' trip through the per-tile partials) disappear, and
-// clusters drift apart in time so that one group's selection overlaps another group's streaming.
+// path (drain, launch, ramp-up, and the scores' trip through the per-tile partials) disappear.
+// One CTA per SM on purpose: with two 128-thread CTAs per SM the hardware placed 256 CTAs on 142 SMs
+// as 114 pairs and 28 singles, a single ran its streaming phases 1.6 times faster than a paired CTA,
+// and every cluster waited for its slowest member.  The cluster size is chosen so that the grid
+// fills the SMs once: 4 CTAs per group from 19 groups up, 8 below.
 // Reference path: cache_hub/retroinfer_cache.py:549-697 (compute).
 #include "ri_wave_attend.cuh"
 #include "ri_wave_select.cuh"
@@ -16,13 +20,20 @@
 namespace ri_wave {
 namespace {
 
-constexpr int kFusedThreads = 128;
-constexpr int kKeysPerThread = 8;                                   // a CTA's slice holds at most 1024 centroids
-constexpr int kMaxSlice = kFusedThreads * kKeysPerThread;
-constexpr int kScoreStride = kMaxSlice + 8;                          // floats per head in shared memory (bank spread)
+constexpr int kFusedThreads = 256;
+constexpr int kFusedWarps = kFusedThreads / 32;
+constexpr int kFusedMaxCentroids = 8192;                             // per group
 constexpr int kScanStages = 2;                                       // the third ring stage holds the scores instead
-constexpr int kScoreOffset = 4 * kScanStages * kStageBytes;          // 64 KB
-static_assert(kAttendCluster == kSelectCluster, "one cluster shape for all phases");
+constexpr int kScoreOffset = kFusedWarps * kScanStages * kStageBytes;   // 128 KB
+constexpr int kFusedRingBytes = kFusedWarps * kStages * kStageBytes;    // 192 KB
+
+template <int CL>
+struct Geom {
+  static constexpr int kMaxSlice = kFusedMaxCentroids / CL;          // centroids a CTA's slice holds at most
+  static constexpr int kKeys = kMaxSlice / kFusedThreads;            // keys per thread: 8 (CL 4) or 4 (CL 8)
+  static constexpr int kScoreStride = kMaxSlice + 8;                 // floats per head in shared memory (bank spread)
+  static_assert(kKeys == 4 || kKeys == 8, "a thread's keys are loaded as one or two 16-byte pieces");
+};
 
 struct FusedArgs {
   SelectArgs sel;
@@ -38,21 +49,32 @@ struct FusedArgs {
   uint4* steady_v_w;
   int persist_off;   // byte offset, behind the ring and the scores, of the lists that outlive the selection
   int cap;           // estimation entries a CTA can keep in shared memory (multiple of 16)
+  int cap_limit;     // test hook: upper limit on `cap` (< 0: none)
+};
+
+// This thread's clusters, fetched before the scan so that their latency is not on the selection's critical path:
+// exact sizes, first row of the first of them, sizes in the 16-bit type.
+template <int KEYS>
+struct ThreadClusters {
+  int cnt[KEYS];
+  int off0;
+  uint32_t szw[KEYS / 2];
 };
 
 // Phase 1 for this CTA's slice [lo, hi) of group g: scores into shared memory (s_sc[h * kScoreStride + e]),
 // and the slice's per-head (max, sum of exponentials) of the rounded scores into part_m/part_s.
-template <int DT>
+template <int DT, int CL>
 __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, int hi, uint8_t* ring, float* s_sc,
                                            float* part_m, float* part_s) {
-  __shared__ float w_m[4][kMaxHeads], w_s[4][kMaxHeads];
+  constexpr int W = kFusedWarps, kScoreStride = Geom<CL>::kScoreStride;
+  __shared__ float w_m[W][kMaxHeads], w_s[W][kMaxHeads];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = lane >> 2, t = lane & 3;
   const int C = f.sel.C, gs = f.sel.gs;
   // stage-major ring as in the attend phase; only stages 0 and 1 are used here
   const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStageBytes + lane * 16;
   const uint8_t* my_ring_ptr = ring + warp * kStageBytes + lane * 16;
-  constexpr int kStageStride = 4 * kStageBytes;
+  constexpr int kStageStride = W * kStageBytes;
   const int n_steps = (hi - lo + 31) / 32;            // 32 centroids per warp step
 
   // piece j*4+kk of a stage: row j*8+r of the step, bytes 16*(t+4kk) — the fragment layout of the scan kernel
@@ -68,10 +90,10 @@ __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, in
     }
   };
 
-  int s_issue = warp;                                  // a warp takes steps warp, warp+4, ...
+  int s_issue = warp;                                  // a warp takes steps warp, warp+W, ...
 #pragma unroll
   for (int st = 0; st < kScanStages; ++st) {
-    if (s_issue < n_steps) { issue(s_issue, st); s_issue += 4; }
+    if (s_issue < n_steps) { issue(s_issue, st); s_issue += W; }
     cp_async_commit();
   }
   uint4 qa[4];
@@ -82,19 +104,26 @@ __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, in
   float m_run = -INFINITY, s_run = 0.f;   // softmax statistics of head r over this warp's centroids
   int stage = 0;
 #pragma unroll 1
-  for (int step = warp; step < n_steps; step += 4) {
+  for (int step = warp; step < n_steps; step += W) {
     cp_async_wait<kScanStages - 1>();
     const uint8_t* src = my_ring_ptr + stage * kStageStride;
     const int base = lo + step * 32;
+    // the stage goes to registers and is refilled at once (the same lane wrote it and reads it), so that two stages
+    // are in flight while this one is worked on
+    uint4 kb[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) kb[i] = *reinterpret_cast<const uint4*>(src + i * 512);
+    if (s_issue < n_steps) { issue(s_issue, stage); s_issue += W; }
+    cp_async_commit();
+    stage ^= 1;
     float rv[4][2];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        const uint4 kb = *reinterpret_cast<const uint4*>(src + (j * 4 + kk) * 512);
-        Elem<DT>::mma16816(acc, qa[kk].x, 0u, qa[kk].y, 0u, kb.x, kb.y);
-        Elem<DT>::mma16816(acc, qa[kk].z, 0u, qa[kk].w, 0u, kb.z, kb.w);
+        Elem<DT>::mma16816(acc, qa[kk].x, 0u, qa[kk].y, 0u, kb[j * 4 + kk].x, kb[j * 4 + kk].y);
+        Elem<DT>::mma16816(acc, qa[kk].z, 0u, qa[kk].w, 0u, kb[j * 4 + kk].z, kb[j * 4 + kk].w);
       }
       const int c0 = base + j * 8 + 2 * t;
       const float v0 = f.alpha * acc[0], v1 = f.alpha * acc[1];
@@ -106,9 +135,6 @@ __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, in
       rv[j][0] = ok ? Elem<DT>::round(v0) : -INFINITY;
       rv[j][1] = ok ? Elem<DT>::round(v1) : -INFINITY;
     }
-    if (s_issue < n_steps) { issue(s_issue, stage); s_issue += 4; }
-    cp_async_commit();
-    stage ^= 1;
 
     float mx = -INFINITY;
 #pragma unroll
@@ -131,32 +157,71 @@ __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, in
   __syncthreads();
   if (tid < kMaxHeads) {
     const int h = tid;
-    const float M = fmaxf(fmaxf(w_m[0][h], w_m[1][h]), fmaxf(w_m[2][h], w_m[3][h]));
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < W; ++w) M = fmaxf(M, w_m[w][h]);
     float S = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w)
+    for (int w = 0; w < W; ++w)
       if (w_m[w][h] > -INFINITY) S += w_s[w][h] * exp2f((w_m[w][h] - M) * RI_LOG2E);
     part_m[h] = M;
     part_s[h] = S;
   }
 }
 
+// Exclusive scan of two 64-bit values per thread at once (one pair of block barriers for both).
+template <int THREADS>
+__device__ __forceinline__ void block_scan2(uint64_t& a, uint64_t& b, uint64_t (*warp_sums)[2]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t ia = a, ib = b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint64_t na = __shfl_up_sync(0xffffffffu, ia, o), nb = __shfl_up_sync(0xffffffffu, ib, o);
+    if (lane >= o) { ia += na; ib += nb; }
+  }
+  __syncthreads();   // protects warp_sums from its previous use
+  if (lane == 31) { warp_sums[warp][0] = ia; warp_sums[warp][1] = ib; }
+  __syncthreads();
+  uint64_t ba = 0, bb = 0;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w)
+    if (w < warp) { ba += warp_sums[w][0]; bb += warp_sums[w][1]; }
+  a = ba + ia - a;
+  b = bb + ib - b;
+}
+
+// Where a cut falls in a histogram of 256 bins scanned from the top (bin 255 = largest keys): the bin, then the
+// keys above that bin and the keys in it — cluster-wide, in the CTAs of lower rank, in this CTA.
+struct CutBin { int bin, above_g, above_l, above_m, at_g, at_l, at_m; };
+
+__device__ __forceinline__ void note_cut(CutBin* out, int bin, uint64_t pre, uint64_t v, int k) {
+  const int ag = (int)(pre & 0xffffu), cg_ = (int)(v & 0xffffu);
+  if (ag < k && ag + cg_ >= k) {
+    out->bin = bin; out->above_g = ag; out->above_l = (int)((pre >> 16) & 0xffffu); out->above_m = (int)((pre >> 32) & 0xffffu);
+    out->at_g = cg_; out->at_l = (int)((v >> 16) & 0xffffu); out->at_m = (int)((v >> 32) & 0xffffu);
+  }
+}
 // Phase 2.  The arithmetic and the tie rules are those of the selection body in ri_wave_select.cuh;
-// the organisation differs: a thread keeps its eight keys in registers, the scores come from shared
-// memory, the positions in the compacted lists follow from ONE packed block scan plus closed forms
-// (the counts of the lower-ranked CTAs are summed from their histograms, ties are taken in id
-// order, so "ties taken before me" = min(ties before me, ties to take)), the P retrieval
-// candidates stay with their owners until every CTA pulls a copy, and every CTA ranks them and applies the
-// page budget on its own copy.  Four cluster barriers instead of six.
+// the organisation differs: a thread keeps its keys in registers, the scores come from shared
+// memory, and every histogram is scanned as packed triples (cluster-wide count | count in the CTAs of
+// lower rank | count in this CTA), so that one scan per radix level yields the cut AND what this CTA
+// needs to place its own entries: how many selected keys, and how many ties on each cut, the CTAs of
+// lower rank hold (they hold the lower ids, and ties are taken in id order: "ties taken before me" =
+// min(ties before me, ties to take)).  The positions in the compacted lists then follow from ONE more
+// packed block scan plus closed forms.  The P retrieval candidates stay with their owners until every
+// CTA pulls a copy, and every CTA ranks them and applies the page budget on its own copy.
+// Three cluster barriers (two histogram levels, candidates) and one split barrier.
 // What the attend phase needs stays in shared memory (`ll`): this CTA's own estimation entries, the kept
 // clusters' row ranges and this CTA's share of the exact steps (balanced against the estimation work
 // every CTA has).  Returns true when that form is usable; false (some CTA holds more estimation entries
 // than its list takes) after writing the global lists that the stand-alone attend body reads instead.
-template <int DT>
+template <int DT, int CL>
 __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int rank, int lo, int n_loc, uint8_t* dyn,
                                                   const float* s_sc, const float* s_max, const float* s_inv,
-                                                  int static_len, LocalLists& ll) {
-  constexpr int T = kFusedThreads;
+                                                  int static_len, const ThreadClusters<Geom<CL>::kKeys>& tc,
+                                                  LocalLists& ll) {
+  constexpr int T = kFusedThreads, KEYS = Geom<CL>::kKeys, kScoreStride = Geom<CL>::kScoreStride;
+  static_assert(T == 256, "one histogram bin per thread");
   const SelectArgs& a = f.sel;
   cg::cluster_group cluster = cg::this_cluster();
   uint4* own = reinterpret_cast<uint4*>(dyn);           // [p_pad] this CTA's retrieval candidates, in id order:
@@ -176,64 +241,65 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   float* est_sc = est_wt + f.cap;                                        // [gs][cap]
   uint16_t* est_idx = reinterpret_cast<uint16_t*>(est_sc + (size_t)a.gs * f.cap);   // [cap]
 
-  // histograms of 256 bins, two 16-bit counters per word (bin 2w low, bin 2w+1 high; a slice holds <= 1024 keys)
-  __shared__ uint32_t hist1[128], hist2a[128], hist2b[128];
-  __shared__ __align__(16) int s_cnt[4];          // this CTA's keys above the K cut | above the P cut | on the K cut | on the P cut
-  __shared__ int s_before[4];       // the same four, summed over the CTAs of lower rank
+  __shared__ uint32_t hist1[256], hist2a[256], hist2b[256];   // bin 255 = largest keys
+  __shared__ CutBin fk, fp, lk, lp;   // high byte of the K and P cuts, then their low bytes
   __shared__ int s_share[4];        // this CTA's exact steps [lo, hi), its estimation entries, whether the lists fit
-  __shared__ int s_nret[kSelectCluster], s_nest[kSelectCluster];   // every CTA's candidates / estimation entries
-  __shared__ int fk[3], fp[3], lk[3], lp[3];
+  __shared__ int s_nret[CL], s_nest[CL];   // every CTA's candidates / estimation entries
   __shared__ uint32_t warp_sums[T / 32];
   __shared__ uint64_t warp_sums64[T / 32];
+  __shared__ uint64_t warp_sums2[T / 32][2];
   __shared__ __align__(16) int s_keep, s_rows;
   __shared__ __align__(8) int s_pub[2];   // this CTA's retrieval candidates, estimation entries
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = a.C, gs = a.gs;
-  if (tid < 128) { hist1[tid] = 0; hist2a[tid] = 0; hist2b[tid] = 0; }
-  if (tid < 3) { fk[tid] = 0; fp[tid] = 0; lk[tid] = 0; lp[tid] = 0; }
+  hist1[tid] = 0; hist2a[tid] = 0; hist2b[tid] = 0;
+  if (tid == 0) {
+    const CutBin z = {0, 0, 0, 0, 0, 0, 0};
+    fk = z; fp = z; lk = z; lp = z;
+  }
   __syncthreads();
 
-  // ---- keys of this thread's eight centroids (ids lo + 8*tid ..), first-level histogram ----
-  const int e0 = tid * kKeysPerThread;
-  const bool live = e0 < n_loc;                  // slices are multiples of 8: all eight or none
+  // ---- keys of this thread's centroids (ids lo + KEYS*tid ..), first-level histogram ----
+  const int e0 = tid * KEYS;
+  const bool live = e0 < n_loc;                  // slices are multiples of 8: all of a thread's keys or none
   const int64_t gc = (int64_t)g * C + lo + e0;
-  uint16_t key[kKeysPerThread];
-  int cnt[kKeysPerThread], off[kKeysPerThread];
-  uint4 sz = make_uint4(0u, 0u, 0u, 0u);
+  uint16_t key[KEYS];
+  int cnt[KEYS], off[KEYS];
 #pragma unroll
-  for (int i = 0; i < kKeysPerThread; ++i) { key[i] = 0; cnt[i] = 0; off[i] = 0; }
+  for (int i = 0; i < KEYS; ++i) { key[i] = 0; cnt[i] = 0; off[i] = 0; }
   if (live) {
-    const int4 c0 = *reinterpret_cast<const int4*>(a.count + gc), c1 = *reinterpret_cast<const int4*>(a.count + gc + 4);
-    cnt[0] = c0.x; cnt[1] = c0.y; cnt[2] = c0.z; cnt[3] = c0.w; cnt[4] = c1.x; cnt[5] = c1.y; cnt[6] = c1.z; cnt[7] = c1.w;
+    int run = tc.off0;
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i) off[i] = a.offset[(int64_t)g * (C + 1) + lo + e0 + i];
-    sz = *reinterpret_cast<const uint4*>(a.size_dt + gc);
-    float dist[kKeysPerThread];
+    for (int i = 0; i < KEYS; ++i) { cnt[i] = tc.cnt[i]; off[i] = run; run += cnt[i]; }
+    float dist[KEYS];
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i) dist[i] = 0.f;
+    for (int i = 0; i < KEYS; ++i) dist[i] = 0.f;
 #pragma unroll
     for (int h = 0; h < kMaxHeads; ++h)
       if (h < gs) {
-        const float4 s0 = *reinterpret_cast<const float4*>(s_sc + h * kScoreStride + e0);
-        const float4 s1 = *reinterpret_cast<const float4*>(s_sc + h * kScoreStride + e0 + 4);
-        const float sv[kKeysPerThread] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-        for (int i = 0; i < kKeysPerThread; ++i)
-          dist[i] += Elem<DT>::round(exp2f((Elem<DT>::round(sv[i]) - s_max[h]) * RI_LOG2E) * s_inv[h]);
+        for (int q4 = 0; q4 < KEYS / 4; ++q4) {
+          const float4 s4 = *reinterpret_cast<const float4*>(s_sc + h * kScoreStride + e0 + 4 * q4);
+          const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dist[4 * q4 + i] += Elem<DT>::round(exp2f((Elem<DT>::round(sv[i]) - s_max[h]) * RI_LOG2E) * s_inv[h]);
+        }
       }
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i) {
+    for (int i = 0; i < KEYS; ++i) {
       uint16_t b = Elem<DT>::bits(dist[i]);
       if (cnt[i] == 0) b = DT == RI_BF16 ? 0xFF7Fu : 0xFBFFu;   // most negative finite value
       key[i] = ri_ordered_key(b);
-      atomicAdd(&hist1[key[i] >> 9], 1u << (16 * ((key[i] >> 8) & 1)));
+      atomicAdd(&hist1[key[i] >> 8], 1u);
     }
     if (f.views) {
-      uint4 kw;
-      kw.x = key[0] | ((uint32_t)key[1] << 16); kw.y = key[2] | ((uint32_t)key[3] << 16);
-      kw.z = key[4] | ((uint32_t)key[5] << 16); kw.w = key[6] | ((uint32_t)key[7] << 16);
-      *reinterpret_cast<uint4*>(a.dist_keys + gc) = kw;
+      uint32_t kw[KEYS / 2];
+#pragma unroll
+      for (int i = 0; i < KEYS / 2; ++i) kw[i] = key[2 * i] | ((uint32_t)key[2 * i + 1] << 16);
+      if constexpr (KEYS == 8) *reinterpret_cast<uint4*>(a.dist_keys + gc) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+      else *reinterpret_cast<uint2*>(a.dist_keys + gc) = make_uint2(kw[0], kw[1]);
     }
   }
   __syncthreads();
@@ -241,89 +307,72 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   cluster.sync();
   RI_FT(4);
 
-  // ---- high byte of the two cuts ----
-  // Thread tid looks after bins 255-2*tid and 254-2*tid, i.e. word 127-tid of the packed histograms:
-  // cluster-wide sums straight from the eight CTAs' words into registers, one packed scan to find the bins.
+  // ---- high byte of the two cuts: thread tid looks after bin 255 - tid ----
   const int K = a.P + a.E;
-  const int my_word = 127 - tid;
+  const int my_bin = 255 - tid;
   {
-    uint32_t w[kSelectCluster];
+    uint32_t w[CL];
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) w[rr] = cluster.map_shared_rank(hist1, rr)[my_word];
-    uint32_t sum = 0;                       // no carry between the halves: a group holds < 65536 keys
+    for (int rr = 0; rr < CL; ++rr) w[rr] = cluster.map_shared_rank(hist1, rr)[my_bin];
+    uint32_t sum = 0, lower = 0;
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) sum += w[rr];
-    const uint32_t mine = hist1[my_word];
-    const int g2[2] = {(int)(sum >> 16), (int)(sum & 0xffffu)}, l2[2] = {(int)(mine >> 16), (int)(mine & 0xffffu)};
-    find_bins_regs<T>(g2, l2, K, fk, g2, l2, a.P, fp, warp_sums64);
+    for (int rr = 0; rr < CL; ++rr) { sum += w[rr]; lower += rr < rank ? w[rr] : 0u; }
+    const uint64_t v = (uint64_t)sum | ((uint64_t)lower << 16) | ((uint64_t)hist1[my_bin] << 32);
+    uint64_t total;
+    const uint64_t pre = block_scan<T, uint64_t>(v, warp_sums64, total);
+    note_cut(&fk, my_bin, pre, v, K);
+    note_cut(&fp, my_bin, pre, v, a.P);
+    __syncthreads();
   }
-  const int binK = fk[0], binP = fp[0];
+  const int binK = fk.bin, binP = fp.bin;
 
   // ---- low byte ----
   if (live) {
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i) {
-      const uint32_t inc = 1u << (16 * (key[i] & 1));
-      if ((key[i] >> 8) == binK) atomicAdd(&hist2a[(key[i] & 255) >> 1], inc);
-      if ((key[i] >> 8) == binP) atomicAdd(&hist2b[(key[i] & 255) >> 1], inc);
+    for (int i = 0; i < KEYS; ++i) {
+      if ((key[i] >> 8) == binK) atomicAdd(&hist2a[key[i] & 255], 1u);
+      if ((key[i] >> 8) == binP) atomicAdd(&hist2b[key[i] & 255], 1u);
     }
   }
   __syncthreads();
   cluster.sync();
   RI_FT(5);
   {
-    uint32_t wa[kSelectCluster], wb[kSelectCluster];
+    uint32_t wa[CL], wb[CL];
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) {
-      wa[rr] = cluster.map_shared_rank(hist2a, rr)[my_word];
-      wb[rr] = cluster.map_shared_rank(hist2b, rr)[my_word];
+    for (int rr = 0; rr < CL; ++rr) {
+      wa[rr] = cluster.map_shared_rank(hist2a, rr)[my_bin];
+      wb[rr] = cluster.map_shared_rank(hist2b, rr)[my_bin];
     }
-    uint32_t sa = 0, sb = 0;
+    uint32_t sa = 0, sb = 0, la = 0, lb = 0;
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) { sa += wa[rr]; sb += wb[rr]; }
-    const uint32_t ma = hist2a[my_word], mb = hist2b[my_word];
-    const int ga[2] = {(int)(sa >> 16), (int)(sa & 0xffffu)}, la[2] = {(int)(ma >> 16), (int)(ma & 0xffffu)};
-    const int gb[2] = {(int)(sb >> 16), (int)(sb & 0xffffu)}, lb[2] = {(int)(mb >> 16), (int)(mb & 0xffffu)};
-    find_bins_regs<T>(ga, la, K - fk[1], lk, gb, lb, a.P - fp[1], lp, warp_sums64);
+    for (int rr = 0; rr < CL; ++rr) {
+      sa += wa[rr]; sb += wb[rr];
+      la += rr < rank ? wa[rr] : 0u; lb += rr < rank ? wb[rr] : 0u;
+    }
+    const uint64_t va = (uint64_t)sa | ((uint64_t)la << 16) | ((uint64_t)hist2a[my_bin] << 32);
+    const uint64_t vb = (uint64_t)sb | ((uint64_t)lb << 16) | ((uint64_t)hist2b[my_bin] << 32);
+    uint64_t pa = va, pb = vb;
+    block_scan2<T>(pa, pb, warp_sums2);
+    note_cut(&lk, my_bin, pa, va, K - fk.above_g);
+    note_cut(&lp, my_bin, pb, vb, a.P - fp.above_g);
+    __syncthreads();
   }
-  const int lowK = lk[0], lowP = lp[0];
   RI_FT(14);
-  const uint16_t TK = (uint16_t)((binK << 8) | lowK), TP = (uint16_t)((binP << 8) | lowP);
-  const int needK = K - fk[1] - lk[1];      // how many keys equal to TK are taken (cluster-wide)
-  const int needP = a.P - fp[1] - lp[1];
-
-  // keys above the cuts, and keys on them, in the CTAs of lower rank (they hold the lower ids): every CTA
-  // publishes its own four counts, eight lanes fetch them, the warp adds up those of lower rank
-  if (tid == 0) {
-    s_cnt[0] = fk[2] + lk[2];
-    s_cnt[1] = fp[2] + lp[2];
-    s_cnt[2] = (int)((hist2a[lowK >> 1] >> (16 * (lowK & 1))) & 0xffffu);
-    s_cnt[3] = (int)((hist2b[lowP >> 1] >> (16 * (lowP & 1))) & 0xffffu);
-  }
-  __syncthreads();
-  cluster.sync();
-  if (warp == 0) {
-    int4 c = make_int4(0, 0, 0, 0);
-    if (lane < rank) c = *reinterpret_cast<const int4*>(cluster.map_shared_rank(s_cnt, lane));   // rank <= 7
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
-      c.x += __shfl_xor_sync(0xffffffffu, c.x, o); c.y += __shfl_xor_sync(0xffffffffu, c.y, o);
-      c.z += __shfl_xor_sync(0xffffffffu, c.z, o); c.w += __shfl_xor_sync(0xffffffffu, c.w, o);
-    }
-    if (lane == 0) { s_before[0] = c.x; s_before[1] = c.y; s_before[2] = c.z; s_before[3] = c.w; }
-  }
-  __syncthreads();
-  RI_FT(15);
-  const int tieK_before = s_before[2], tieP_before = s_before[3];
-  const int inK_before = s_before[0] + min(needK, tieK_before);
-  const int inP_before = s_before[1] + min(needP, tieP_before);
+  const uint16_t TK = (uint16_t)((binK << 8) | lk.bin), TP = (uint16_t)((binP << 8) | lp.bin);
+  const int needK = K - fk.above_g - lk.above_g;      // how many keys equal to TK are taken (cluster-wide)
+  const int needP = a.P - fp.above_g - lp.above_g;
+  // the CTAs of lower rank: ties on each cut, and selected keys (those above the cut plus the ties they take)
+  const int tieK_before = lk.at_l, tieP_before = lp.at_l;
+  const int inK_before = fk.above_l + lk.above_l + min(needK, tieK_before);
+  const int inP_before = fp.above_l + lp.above_l + min(needP, tieP_before);
   const int remK = max(needK - tieK_before, 0), remP = max(needP - tieP_before, 0);   // ties this CTA and later ones take
 
   // ---- ordered compaction ----
   uint64_t c4 = 0;     // 16-bit counters: above K cut | on K cut | above P cut | on P cut
   if (live) {
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i)
+    for (int i = 0; i < KEYS; ++i)
       c4 += (key[i] > TK ? 1ull : 0ull) | (key[i] == TK ? 1ull << 16 : 0ull) | (key[i] > TP ? 1ull << 32 : 0ull) |
             (key[i] == TP ? 1ull << 48 : 0ull);
   }
@@ -332,12 +381,11 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   int gtK = (int)(pre & 0xffffu), eqK = (int)((pre >> 16) & 0xffffu);
   int gtP = (int)((pre >> 32) & 0xffffu), eqP = (int)(pre >> 48);
   RI_FT(6);
-  uint32_t est_mask = 0;     // which of the eight are estimation entries, and their positions in this CTA's list
-  int est_lp[kKeysPerThread];
+  uint32_t est_mask = 0;     // which of this thread's keys are estimation entries, and their positions in this CTA's list
+  int est_lp[KEYS];
   if (live) {
-    const uint32_t szw[4] = {sz.x, sz.y, sz.z, sz.w};
 #pragma unroll
-    for (int i = 0; i < kKeysPerThread; ++i) {
+    for (int i = 0; i < KEYS; ++i) {
       const bool inK = key[i] > TK || (key[i] == TK && eqK < remK);
       const bool inP = key[i] > TP || (key[i] == TP && eqP < remP);
       const int posK = gtK + min(eqK, remK), posP = gtP + min(eqP, remP);   // taken keys before this one, in this CTA
@@ -347,43 +395,43 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
                                (uint32_t)off[i], 0u);
       } else if (inK) {
         est_mask |= 1u << i;
-        const int lp = est_lp[i];
-        if (lp < f.cap) {
-          est_idx[lp] = (uint16_t)(e0 + i);
-          est_wt[lp] = Elem<DT>::from_bits((uint16_t)(szw[i >> 1] >> (16 * (i & 1))));
+        const int lpos = est_lp[i];
+        if (lpos < f.cap) {
+          est_idx[lpos] = (uint16_t)(e0 + i);
+          est_wt[lpos] = Elem<DT>::from_bits((uint16_t)(tc.szw[i >> 1] >> (16 * (i & 1))));
 #pragma unroll
           for (int h = 0; h < kMaxHeads; ++h)
-            if (h < gs) est_sc[h * f.cap + lp] = s_sc[h * kScoreStride + e0 + i] * RI_LOG2E;
+            if (h < gs) est_sc[h * f.cap + lpos] = s_sc[h * kScoreStride + e0 + i] * RI_LOG2E;
         }
       }
       gtK += key[i] > TK; eqK += key[i] == TK; gtP += key[i] > TP; eqP += key[i] == TP;
     }
   }
+  const int my_ret = (int)((c4_total >> 32) & 0xffffu) + min((int)(c4_total >> 48), remP);
+  const int my_est = (int)(c4_total & 0xffffu) + min((int)((c4_total >> 16) & 0xffffu), remK) - my_ret;
   if (tid == 0) {
-    const int n_ret = (int)((c4_total >> 32) & 0xffffu) + min((int)(c4_total >> 48), remP);
-    const int n_in = (int)(c4_total & 0xffffu) + min((int)((c4_total >> 16) & 0xffffu), remK);
-    s_pub[0] = n_ret;
-    s_pub[1] = n_in - n_ret;
+    s_pub[0] = my_ret;
+    s_pub[1] = my_est;
   }
   __syncthreads();
   cluster.sync();       // every CTA's candidate list, estimation list and counts are complete
   RI_FT(7);
 
   // ---- every CTA: pull the P candidates of the group, rank them, page budget, place in the row list ----
-  if (tid < kSelectCluster) {
+  if (tid < CL) {
     const int2 pub = *reinterpret_cast<const int2*>(cluster.map_shared_rank(s_pub, tid));
     s_nret[tid] = pub.x;
     s_nest[tid] = pub.y;
   }
   __syncthreads();
   {
-    int nret[kSelectCluster];
+    int nret[CL];
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) nret[rr] = s_nret[rr];
+    for (int rr = 0; rr < CL; ++rr) nret[rr] = s_nret[rr];
     for (int i = tid; i < a.p_pad; i += T) {
       int src = 0, j = i, lim = nret[0];     // candidate i of the group = candidate j of CTA src, which holds lim
 #pragma unroll
-      for (int rr = 0; rr < kSelectCluster - 1; ++rr)
+      for (int rr = 0; rr < CL - 1; ++rr)
         if (src == rr && j >= nret[rr]) { j -= nret[rr]; ++src; lim = nret[rr + 1]; }
       uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding compares below every real candidate
       if (i < a.P && j < lim) v = cluster.map_shared_rank(own, src)[j];
@@ -395,23 +443,36 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   RI_FT(16);
   // Page budget (wave_buffer_cpu.cpp:207-216): the clusters are taken in rank order while their pages fit.
   // When ALL P candidates fit — the usual case — the order plays no part in what is attended, so unless the
-  // caller wants the ranked ids the ranking is skipped and the rows are laid out in cluster-id order.
+  // caller wants the ranked ids the ranking is skipped and the rows are laid out in cluster-id order: one scan.
   constexpr int kPer = 1024 / T;    // P <= 1024
   int pc[kPer], pages[kPer];
-  uint32_t psum, total, before;
-  auto count_pages = [&](const uint32_t* sizes) {
-    psum = 0;
+  uint32_t before;
+  // pages (low half) and rows (high half) of the candidates in id order, one packed scan
+  uint64_t pr = 0;
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int i = tid * kPer + u;
+    pc[u] = i < a.P ? (int)cand_cnt[i] : 0;
+    pages[u] = (pc[u] + a.page - 1) / a.page;
+    pr += (uint64_t)(uint32_t)pages[u] | ((uint64_t)(uint32_t)pc[u] << 32);
+  }
+  uint64_t pr_total;
+  const uint64_t pr_pre = block_scan<T, uint64_t>(pr, warp_sums64, pr_total);
+  if (!f.views && (int)(uint32_t)pr_total <= a.buffer_pages) {
+    // everything fits: id order serves as the order of the row list, each cluster starts at the rows before it
+    rcnt = cand_cnt;
+    roff = cand_off;
+    uint32_t row_start = (uint32_t)(pr_pre >> 32);
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int i = tid * kPer + u;
-      pc[u] = i < a.P ? (int)sizes[i] : 0;
-      pages[u] = (pc[u] + a.page - 1) / a.page;
-      psum += (uint32_t)pages[u];
+      if (i < a.P) rstart[i] = row_start;
+      row_start += (uint32_t)pc[u];
     }
-    before = block_scan<T, uint32_t>(psum, warp_sums, total);
-  };
-  count_pages(cand_cnt);
-  if (f.views || (int)total > a.buffer_pages) {
+    if (tid == 0) { s_keep = a.P; s_rows = (int)(pr_total >> 32); }
+    RI_FT(17);
+    __syncthreads();
+  } else {
     {
       // rank = number of larger candidates (distinct values: distinct ranks); four lanes share a candidate,
       // each counting over a quarter of the list
@@ -442,13 +503,16 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       }
     }
     __syncthreads();
-    count_pages(rcnt);
-  } else {
-    rcnt = cand_cnt;      // id order serves as the order of the row list
-    roff = cand_off;
-  }
-  RI_FT(17);
-  {
+    uint32_t psum = 0, total;
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int i = tid * kPer + u;
+      pc[u] = i < a.P ? (int)rcnt[i] : 0;
+      pages[u] = (pc[u] + a.page - 1) / a.page;
+      psum += (uint32_t)pages[u];
+    }
+    before = block_scan<T, uint32_t>(psum, warp_sums, total);
+    RI_FT(17);
     // pages are non-negative, so the clusters that fit the budget form a prefix of the order
     bool fits[kPer];
     uint32_t nfit = 0, rsum = 0;
@@ -482,14 +546,15 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   }
   // Share out the exact steps: level the cost units (kCostEst per estimation step a CTA already has,
   // kCostExact per exact step to hand out) so that sum_c max(0, level - e_c) >= X, then cut the exact steps at the
-  // running sums.  Lane c of warp 0 stands for CTA c.  Two rounds of levelling (CTAs above the first level drop
-  // out of the second) are enough in practice; whatever imbalance is left only costs time.
-  if (warp == 0) {
+  // running sums.  Lane c of the last warp stands for CTA c (warp 0 is busy with the loop above for longest).
+  // Two rounds of levelling (CTAs above the first level drop out of the second) are enough in practice; whatever
+  // imbalance is left only costs time.
+  if (warp == T / 32 - 1) {
     const int xs_total = (static_len + rows_kept + 15) / 16;
     const int X = f.att.cost_exact * xs_total;
-    const int n_e = lane < kSelectCluster ? s_nest[lane] : 0;
+    const int n_e = lane < CL ? s_nest[lane] : 0;
     const int e_u = f.att.cost_est * ((n_e + 15) / 16);
-    bool act = lane < kSelectCluster;
+    bool act = lane < CL;
     int level = 0;
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
@@ -501,15 +566,15 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       level = (int)__fdividef((float)(X + sum_e + n - 1), (float)n);
       act = act && e_u <= level;
     }
-    const int x_u = lane < kSelectCluster ? max(0, level - e_u) : 0;
+    const int x_u = lane < CL ? max(0, level - e_u) : 0;
     int incl = x_u;
 #pragma unroll
-    for (int o = 1; o < kSelectCluster; o <<= 1) {
+    for (int o = 1; o < CL; o <<= 1) {
       const int nb = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += nb;
     }
     const int b_lo = min(xs_total, (incl - x_u + f.att.cost_exact - 1) / f.att.cost_exact);
-    const int b_hi = lane == kSelectCluster - 1 ? xs_total : min(xs_total, (incl + f.att.cost_exact - 1) / f.att.cost_exact);
+    const int b_hi = lane == CL - 1 ? xs_total : min(xs_total, (incl + f.att.cost_exact - 1) / f.att.cost_exact);
     int est_max = n_e;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) est_max = max(est_max, __shfl_xor_sync(0xffffffffu, est_max, o));
@@ -528,14 +593,13 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   if (f.views || !local) {
     int est_base = inK_before - inP_before;   // estimation entries in the CTAs of lower rank
     if (est_mask) {
-      const uint32_t szw[4] = {sz.x, sz.y, sz.z, sz.w};
 #pragma unroll
-      for (int i = 0; i < kKeysPerThread; ++i)
+      for (int i = 0; i < KEYS; ++i)
         if (est_mask >> i & 1u) {
           const int pe = est_base + est_lp[i];
           if (pe < a.E) {
             a.est_ids[(int64_t)g * a.e_pad + pe] = lo + e0 + i;
-            a.est_w[(int64_t)g * a.e_pad + pe] = Elem<DT>::from_bits((uint16_t)(szw[i >> 1] >> (16 * (i & 1))));
+            a.est_w[(int64_t)g * a.e_pad + pe] = Elem<DT>::from_bits((uint16_t)(tc.szw[i >> 1] >> (16 * (i & 1))));
 #pragma unroll
             for (int h = 0; h < kMaxHeads; ++h)
               if (h < gs) a.est_s2[((int64_t)g * kMaxHeads + h) * a.e_pad + pe] = s_sc[h * kScoreStride + e0 + i] * RI_LOG2E;
@@ -543,7 +607,7 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
           }
         }
     }
-    constexpr int kWarpsTotal = kSelectCluster * (T / 32);   // the cluster's 32 warps share the kept clusters out
+    constexpr int kWarpsTotal = CL * (T / 32);   // the cluster's warps share the kept clusters out
     for (int i = rank * (T / 32) + warp; i < keep; i += kWarpsTotal) {
       const int o = (int)roff[i], n = (int)rcnt[i], start = (int)rstart[i];
       for (int j = lane; j < n; j += 32)
@@ -567,10 +631,11 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   return local;
 }
 
-template <int DT>
-__global__ void __cluster_dims__(kSelectCluster, 1, 1) __launch_bounds__(kFusedThreads, kCtasPerSm)
+template <int DT, int CL>
+__global__ void __cluster_dims__(CL, 1, 1) __launch_bounds__(kFusedThreads, 1)
 wave_fused_kernel(FusedArgs f) {
   ri_pdl_enter();
+  constexpr int KEYS = Geom<CL>::kKeys;
   extern __shared__ __align__(16) uint8_t ring[];
   __shared__ float part_m[kMaxHeads], part_s[kMaxHeads], s_max[kMaxHeads], s_inv[kMaxHeads];
   cg::cluster_group cluster = cg::this_cluster();
@@ -583,6 +648,33 @@ wave_fused_kernel(FusedArgs f) {
   int static_len;     // fetched now (not where the compiler would sink the load to: the middle of phase 2)
   asm volatile("ld.global.b32 %0, [%1];" : "=r"(static_len) : "l"(f.att.static_len));
 
+  // this thread's clusters (sizes, first row): requested now, needed after the scan
+  ThreadClusters<KEYS> tc;
+  {
+    const int e0 = tid * KEYS;
+    const int64_t gc = (int64_t)g * C + lo + e0;
+    if (e0 < hi - lo) {
+#pragma unroll
+      // volatile: issued here, ahead of the scan, whatever the compiler would prefer
+      for (int q4 = 0; q4 < KEYS / 4; ++q4)
+        asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(tc.cnt[4 * q4]), "=r"(tc.cnt[4 * q4 + 1]), "=r"(tc.cnt[4 * q4 + 2]), "=r"(tc.cnt[4 * q4 + 3])
+                     : "l"(f.sel.count + gc + 4 * q4));
+      asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(tc.off0) : "l"(f.sel.offset + (int64_t)g * (C + 1) + lo + e0));
+      if constexpr (KEYS == 8)
+        asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(tc.szw[0]), "=r"(tc.szw[1]), "=r"(tc.szw[2]), "=r"(tc.szw[3]) : "l"(f.sel.size_dt + gc));
+      else
+        asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(tc.szw[0]), "=r"(tc.szw[1]) : "l"(f.sel.size_dt + gc));
+    } else {
+#pragma unroll
+      for (int i = 0; i < KEYS; ++i) tc.cnt[i] = 0;
+#pragma unroll
+      for (int i = 0; i < KEYS / 2; ++i) tc.szw[i] = 0u;
+      tc.off0 = 0;
+    }
+  }
+
   // the new token's rows go into the steady zone now; the attend phase reads them several cluster barriers later
   if (f.new_k != nullptr && rank == 0 && tid < 32 && static_len >= 1 && static_len <= f.att.steady_stride) {
     const int64_t dst = ((int64_t)g * f.att.steady_stride + static_len - 1) * 16 + (tid & 15);
@@ -592,13 +684,13 @@ wave_fused_kernel(FusedArgs f) {
 
   // ---- phase 1: scores of this CTA's slice ----
   RI_FT(0);
-  scan_slice<DT>(f, g, lo, hi, ring, s_sc, part_m, part_s);
+  scan_slice<DT, CL>(f, g, lo, hi, ring, s_sc, part_m, part_s);
   RI_FT(1);
   cluster.sync();     // the partials of all slices are published
   if (tid < f.sel.gs) {
     float M = -INFINITY, S = 0.f;
 #pragma unroll
-    for (int rr = 0; rr < kSelectCluster; ++rr) {
+    for (int rr = 0; rr < CL; ++rr) {
       const float m = cluster.map_shared_rank(part_m, rr)[tid], sv = cluster.map_shared_rank(part_s, rr)[tid];
       const float Mn = fmaxf(M, m);
       if (Mn > -INFINITY) S = S * exp2f((M - Mn) * RI_LOG2E) + sv * exp2f((m - Mn) * RI_LOG2E);
@@ -611,12 +703,12 @@ wave_fused_kernel(FusedArgs f) {
   // ---- phase 2: selection (its arrays live in the idle ring stages) ----
   RI_FT(2);
   LocalLists ll;
-  const bool local = select_in_cluster<DT>(f, g, rank, lo, hi - lo, ring, s_sc, s_max, s_inv, static_len, ll);
+  const bool local = select_in_cluster<DT, CL>(f, g, rank, lo, hi - lo, ring, s_sc, s_max, s_inv, static_len, tc, ll);
   RI_FT(9);
 
   // ---- phase 3: attention over the estimation and exact rows selected above ----
-  if (local) attend_group<DT, true>(f.att, g, rank, ring, &ll);
-  else attend_group<DT, false>(f.att, g, rank, ring);
+  if (local) attend_group<DT, true, kFusedWarps, CL>(f.att, g, rank, ring, &ll);
+  else attend_group<DT, false, kFusedWarps, CL>(f.att, g, rank, ring);
   RI_FT(13);
 }
 
@@ -646,34 +738,53 @@ __global__ void gather_signal_wait_kernel(uint32_t* const* flag_slots, const uin
   }
 }
 
-// Shared memory one CTA may use when two of them share an SM, minus the kernel's static part.
-template <int DT>
-int dynamic_budget(int* out) {
-  static int cached[64] = {0};
+// Shared memory the kernel's one CTA per SM may use, minus the kernel's static part; and the SM count.
+template <int DT, int CL>
+int dynamic_budget(int* out, int* sms_out) {
+  static int cached[64] = {0}, cached_sms[64] = {0};
   int dev = 0;
   RI_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || cached[dev] == 0) {
-    int per_sm = 0, reserved = 0, optin = 0;
+  const bool track = dev >= 0 && dev < 64;
+  if (!track || cached[dev] == 0) {
+    int per_sm = 0, reserved = 0, optin = 0, sms = 0;
     RI_CUDA_OK(cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
     RI_CUDA_OK(cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev));
     RI_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    RI_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cudaFuncAttributes fa;
-    RI_CUDA_OK(cudaFuncGetAttributes(&fa, wave_fused_kernel<DT>));
-    int budget = per_sm / kCtasPerSm - reserved - (int)fa.sharedSizeBytes;
+    RI_CUDA_OK(cudaFuncGetAttributes(&fa, wave_fused_kernel<DT, CL>));
+    int budget = per_sm - reserved - (int)fa.sharedSizeBytes;
     if (budget > optin - (int)fa.sharedSizeBytes) budget = optin - (int)fa.sharedSizeBytes;
     budget &= ~15;
-    if (dev < 0 || dev >= 64) { *out = budget; return RI_OK; }
+    if (!track) { *out = budget; *sms_out = sms; return RI_OK; }
     cached[dev] = budget;
+    cached_sms[dev] = sms;
   }
   *out = cached[dev];
+  *sms_out = cached_sms[dev];
   return RI_OK;
 }
 
-template <int DT>
+int g_cap_limit = -1;   // ri_wave_test_local_cap
+
+int sm_count(int* out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  RI_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) { *out = cached[dev]; return RI_OK; }
+  int sms = 0;
+  RI_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (dev >= 0 && dev < 64) cached[dev] = sms;
+  *out = sms;
+  return RI_OK;
+}
+
+template <int DT, int CL>
 int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
   FusedArgs f;
   int rc = fill_select_args(p, L, f.sel);
   if (rc != RI_OK) return rc;
+  f.sel.slice = ((p.n_centroids / 8 + CL - 1) / CL) * 8;        // centroids per CTA of this kernel's cluster
   fill_attend_args(p, L, nullptr, f.att);
   f.cent = static_cast<const uint4*>(p.d_centroids);
   f.scores = reinterpret_cast<float*>(static_cast<uint8_t*>(p.d_scratch) + L.scores);
@@ -686,42 +797,46 @@ int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wav
   if (gather) {
     f.att.copies = reinterpret_cast<uint16_t* const*>(gather->d_out_slots);
     f.att.n_copies = gather->n_ranks;
-
   }
-  RI_REQUIRE(fused_supported(p), "the single-kernel path needs n_centroids <= %d", kMaxSlice * kSelectCluster);
+  RI_REQUIRE(fused_supported(p), "the single-kernel path needs n_centroids <= %d", kFusedMaxCentroids);
   RI_REQUIRE((size_t)f.sel.p_pad * 44 <= (size_t)kScoreOffset, "nprobe=%d too large", p.nprobe);
   // dynamic shared memory: [ring | scores (over ring stage 2 and beyond)] [kept-cluster ranges] [estimation lists]
-  int budget = 0;
-  if ((rc = dynamic_budget<DT>(&budget)) != RI_OK) return rc;
-  const int scores_end = kScoreOffset + p.group_size * kScoreStride * (int)sizeof(float);
-  f.persist_off = (int)ri_align_up(scores_end > kRingBytes ? scores_end : kRingBytes, 16);
+  int budget = 0, sms = 0;
+  if ((rc = dynamic_budget<DT, CL>(&budget, &sms)) != RI_OK) return rc;
+  const int scores_end = kScoreOffset + p.group_size * Geom<CL>::kScoreStride * (int)sizeof(float);
+  f.persist_off = (int)ri_align_up(scores_end > kFusedRingBytes ? scores_end : kFusedRingBytes, 16);
   const int ranges = (2 * f.sel.p_pad + 4) * 4;
   const int per_entry = 4 * p.group_size + 4 + 2;
   int cap = (budget - f.persist_off - ranges) / per_entry;
-  if (const char* e = getenv("RI_WAVE_LOCAL_CAP")) cap = cap < atoi(e) ? cap : atoi(e);   // tests: force the global lists
-  cap = cap < 0 ? 0 : (cap > kMaxSlice ? kMaxSlice : cap) & ~15;
+  if (g_cap_limit >= 0 && cap > g_cap_limit) cap = g_cap_limit;
+  cap = cap < 0 ? 0 : (cap > Geom<CL>::kMaxSlice ? Geom<CL>::kMaxSlice : cap) & ~15;
   f.cap = cap;
   const size_t smem = ri_align_up((size_t)f.persist_off + ranges + (size_t)cap * per_entry, 16);
   RI_REQUIRE((int)smem <= budget, "nprobe=%d needs %zu bytes of shared memory per CTA (limit %d)", p.nprobe, smem, budget);
-  RI_CUDA_OK(cudaFuncSetAttribute(wave_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  RI_CUDA_OK(ri_launch_pdl_id(5, wave_fused_kernel<DT>, dim3(kSelectCluster, p.groups), dim3(kFusedThreads), smem, s, f));
+  RI_CUDA_OK(cudaFuncSetAttribute(wave_fused_kernel<DT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  RI_CUDA_OK(ri_launch_pdl_id(5, wave_fused_kernel<DT, CL>, dim3(CL, p.groups), dim3(kFusedThreads), smem, s, f));
   return RI_OK;
 }
 
 }  // namespace
 
-#ifdef RI_FUSED_TRACE
-extern "C" int ri_debug_fused_trace(unsigned long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_ftrace, sizeof(unsigned long long) * n);
-}
-#endif
+bool fused_supported(const ri_wave_layer& p) { return p.n_centroids <= kFusedMaxCentroids; }
 
-bool fused_supported(const ri_wave_layer& p) {
-  return ((p.n_centroids / 8 + kSelectCluster - 1) / kSelectCluster) * 8 <= kMaxSlice;
+// Test hook: cap the estimation entries a CTA keeps in shared memory (0 forces the global lists, a small value the
+// mixed case); negative restores the default.  Not part of the decode interface.
+extern "C" int ri_wave_test_local_cap(int cap) {
+  g_cap_limit = cap;
+  return RI_OK;
 }
 
 int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
-  return p.dtype == RI_BF16 ? launch<RI_BF16>(p, L, s, gather) : launch<RI_F16>(p, L, s, gather);
+  // cluster size: the largest of 8 and 4 CTAs per group whose grid still fits the SMs at one CTA each
+  int sms = 0;
+  const int rc = sm_count(&sms);
+  if (rc != RI_OK) return rc;
+  const bool wide = p.groups * 8 <= sms;
+  if (p.dtype == RI_BF16) return wide ? launch<RI_BF16, 8>(p, L, s, gather) : launch<RI_BF16, 4>(p, L, s, gather);
+  return wide ? launch<RI_F16, 8>(p, L, s, gather) : launch<RI_F16, 4>(p, L, s, gather);
 }
 
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s) {

@@ -13,20 +13,9 @@ constexpr int kMaxHeads = 8;        // GQA group size limit (N dimension of the 
 constexpr int kAttendMaxCtas = 512; // persistent attend CTAs (2 per SM) the scratch is sized for; 4 warps each
 constexpr int kAttendMaxGroups = 4096;
 
-// Timing build (-DRI_FUSED_TRACE): thread 0 of every CTA of the single-kernel path stamps the global
-// timer at phase boundaries; ri_debug_fused_trace() copies the stamps out.  Compiled out otherwise.
-#ifdef RI_FUSED_TRACE
-static __device__ unsigned long long g_ftrace[4096 * 64];
-__device__ __forceinline__ void ri_ft(int k) {
-  if (threadIdx.x == 0 && gridDim.y * gridDim.x <= 4096) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 64 + k] = t;
-    g_ftrace[(blockIdx.y * gridDim.x + blockIdx.x) * 64 + 32 + k] = (unsigned long long)clock64();
-  }
-}
-#define RI_FT(k) ri_ft(k)
-#else
+// Phase markers of the single-kernel path.  They compile to nothing; a timing build may define RI_FT(k)
+// before this header to stamp a clock at each marker.
+#ifndef RI_FT
 #define RI_FT(k)
 #endif
 
@@ -64,7 +53,9 @@ int launch_scan(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 // `eb` (optional): attend over a dense execution buffer instead of the cluster-contiguous store.
 struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
-int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr);
+// `gather` (optional): also store the output into every rank's gather buffer (several GPUs).
+int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr,
+                  const ri_wave_gather* gather = nullptr);
 int launch_weighted_decoding(const void* q, const void* k, const void* v, const void* weights, const int32_t* seqlens,
                              const void* prev_out, const float* prev_lse, void* out, float* lse_out, int groups,
                              int group_size, int64_t stride, int dtype, cudaStream_t s);

@@ -2,7 +2,8 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py <reference checkout>      (or RI_REFERENCE_ROOT in the environment)
+    python tests/golden/make_golden.py <reference checkout> [all|kmeans|kmeans-missing|wave]
+    (the checkout may also be named by RI_REFERENCE_ROOT in the environment)
 
 * ``kmeans_*.pt`` — outputs of the reference's own ``cache_hub/kmeans.py``
   (``segment_k_means``) executed unmodified on CPU tensors under the Triton
@@ -45,6 +46,10 @@ KMEANS_CASES = {
     # planted < 0: only -planted distinct key rows, repeated -> duplicate initial
     # centroids, so many clusters stay empty (edge case: masked centroid store).
     "kmeans_duplicates_empty": (2, 700, 64, 1, 5, 14, -37),
+    # one and two iterations: both sides start from the same centroids, so every assignment that differs
+    # from the reference's has to be a tie (strict parity, no drift to allow for)
+    "kmeans_iter1": (2, 1200, 64, 2, 1, 15, 0),
+    "kmeans_iter2": (2, 1200, 64, 2, 2, 16, 0),
 }
 
 
@@ -62,12 +67,14 @@ def kmeans_inputs(heads, tokens, seed, planted, dtype=torch.float16):
     return k, v, k - mean
 
 
-def make_kmeans(reference_root: str):
+def make_kmeans(reference_root: str, only_missing: bool = False):
     spec = importlib.util.spec_from_file_location(
         "ref_kmeans", os.path.join(reference_root, "cache_hub", "kmeans.py"))
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
     for name, (heads, tokens, cents, segs, iters, seed, planted) in KMEANS_CASES.items():
+        if only_missing and os.path.exists(os.path.join(HERE, name + ".pt")):
+            continue
         k, v, centred = kmeans_inputs(heads, tokens, seed, planted)
         cen, vsum, clusters, sizes = ref.segment_k_means(centred, v, cents, num_iters=iters, num_segments=segs)
         assign = torch.full((heads, tokens), -1, dtype=torch.int32)
@@ -154,9 +161,11 @@ def make_wave_buffer():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RI_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RI_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py <reference checkout> [all|kmeans|kmeans-missing|wave]   (or set RI_REFERENCE_ROOT)")
     which = sys.argv[2] if len(sys.argv) > 2 else "all"
-    if which in ("all", "kmeans"):
-        make_kmeans(root)
+    if which in ("all", "kmeans", "kmeans-missing"):
+        make_kmeans(root, only_missing=which == "kmeans-missing")
     if which in ("all", "wave"):
         make_wave_buffer()

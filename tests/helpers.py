@@ -116,3 +116,44 @@ def to_gpu_layer(case: Case, cpu: dict, static_len: int, want_ids: bool = True):
 
 def queries(case: Case, seed: int = 100) -> torch.Tensor:
     return make_queries(case.batch, case.q_heads, 128, seed=seed, dtype=case.dtype)
+
+
+def gpu_built_layer(batch: int, kv_heads: int, group_size: int, n_clustered: int, n_centroids: int, n_segment: int,
+                    nprobe: int, n_estimate: int, seed: int = 0, iters: int = 3, want_ids: bool = True,
+                    n_layers: int = 1):
+    """Layers whose index is built on the GPU by ``ri_kmeans_build`` (sizes the CPU oracle would take too long to
+    cluster).  Returns (list of WaveIndexLayer over the same tensors, dict of the tensors, queries [B, 1, Hq, 128])."""
+    from retrievalattention_b200 import wave
+    from retrievalattention_b200.cache_hub.kmeans import build_index
+
+    dev = torch.device("cuda", 0)
+    context = n_clustered + SINK + RECENT
+    parts = []
+    raw = []
+    for b in range(batch):
+        k, v = make_kv(kv_heads, context, 128, seed=seed * 1000 + b, device=dev)
+        k, v = k[0].transpose(0, 1).contiguous(), v[0].transpose(0, 1).contiguous()
+        r = build_index(k[:, SINK:SINK + n_clustered].contiguous(), v[:, SINK:SINK + n_clustered].contiguous(),
+                        n_centroids, n_segment, iters)
+        assert int(r["error"]) == 0
+        parts.append(r)
+        raw.append((k, v))
+    cat = lambda name: torch.cat([p[name] for p in parts], 0).contiguous()          # noqa: E731
+    g = batch * kv_heads
+    stride = SINK + RECENT + 8
+    steady_k = torch.zeros((g, stride, 128), dtype=torch.bfloat16, device=dev)
+    steady_v = torch.zeros_like(steady_k)
+    raw_k, raw_v = torch.cat([r[0] for r in raw], 0), torch.cat([r[1] for r in raw], 0)
+    steady_k[:, :SINK], steady_v[:, :SINK] = raw_k[:, :SINK], raw_v[:, :SINK]
+    steady_k[:, SINK:SINK + RECENT] = raw_k[:, SINK + n_clustered:]
+    steady_v[:, SINK:SINK + RECENT] = raw_v[:, SINK + n_clustered:]
+    pages = max(nprobe * 4, 16) * math.ceil((n_clustered // n_centroids) / 8)
+    shape = wave.WaveShape(g, group_size, n_centroids, nprobe, n_estimate, 8, pages, n_clustered, stride, torch.bfloat16)
+    t = dict(centroids=cat("centroids"), value_sum=cat("value_sum"), cluster_size=cat("cluster_size"),
+             cluster_count=cat("cluster_count"), cluster_offset=cat("cluster_offset"), keys=cat("keys"),
+             values=cat("values"), steady_keys=steady_k, steady_values=steady_v)
+    static_len = torch.full((1,), SINK + RECENT, dtype=torch.int32, device=dev)
+    layers = [wave.WaveIndexLayer(shape, want_ids=want_ids, static_len=static_len, scratch=wave.new_scratch(shape, dev), **t)
+              for _ in range(n_layers)]
+    q = make_queries(batch, kv_heads * group_size, 128, seed=seed + 100, device=dev)
+    return layers, t, q

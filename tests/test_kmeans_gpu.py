@@ -1,10 +1,17 @@
 """Parity of the CUDA clustering (tcgen05 assignment GEMM + bucket + update + layout, through the
 C ABI) against (a) the fixtures recorded from the reference's own kmeans.py and (b) the CPU oracle.
 
-Bar: assignments, counts and member lists bit-exact except for tokens whose two best inner
-products tie within 1e-3 (relative) — the tensor core accumulates the 128 products in a different
-order than the CPU; centroids and value sums within one ulp of the 16-bit dtype wherever the
-member sets agree."""
+Bar (cluster assignments bit-exact except ties):
+
+* one or two Lloyd iterations — both sides start from the same centroids — EVERY assignment that differs
+  must be a tie: the two clusters' inner products with the token, evaluated on the oracle's centroids of
+  the last assignment pass, differ by no more than the noise a tie can hide (fp32 accumulation order
+  with identical centroids: 1e-5 of |x||c|; one 16-bit rounding step of a centroid after an update:
+  2 ulp of |x||c|);
+* more iterations: a flipped tie moves a centroid by a rounding step and the runs drift apart from
+  there, which no tie rule at the end can excuse; the stated bound is <= 1 % of the assignments and
+  >= 97 % of the cluster sizes equal, with centroids and value sums within one ulp of the 16-bit
+  dtype wherever the sizes agree."""
 import os
 import sys
 
@@ -20,14 +27,44 @@ from retrievalattention_b200.synthetic import make_kv  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(HERE, "golden")
+DRIFT_ASSIGN, DRIFT_SIZES = 0.01, 0.97
 
 
-def tie_excused(data, centroids, a, b, band=1e-3):
-    """True where assignment a and b differ only between clusters whose scores tie."""
+def last_pass_centroids(centred, cents, iters, segs):
+    """The oracle's centroids that the LAST assignment pass of ``segment_k_means`` compares against
+    (cache_hub/kmeans.py:232-248): the evenly spaced initial rows, moved by iters - 1 segmented passes."""
+    groups, n, d = centred.shape
+    cen = torch.index_select(centred, 1, okm.initial_centroid_indices(n, cents))
+    n_seg, c_seg = n // segs, cents // segs
+    data = centred[:, :n_seg * segs].reshape(-1, n_seg, d)
+    cen = cen.reshape(-1, c_seg, d)
+    for _ in range(iters - 1):
+        cen, _, _ = okm.train_step(data, cen, normalize=True)
+    return cen.reshape(groups, cents, d)
+
+
+def tie_margin(data, centroids, a, b):
+    """|x.c_a - x.c_b| relative to |x| times the mean norm of the two centroids."""
     ip = torch.bmm(data.float(), centroids.float().transpose(1, 2))
     sa = torch.gather(ip, 2, a.long()[..., None])[..., 0]
     sb = torch.gather(ip, 2, b.long()[..., None])[..., 0]
-    return (sa - sb).abs() <= band * torch.maximum(sa.abs(), sb.abs()).clamp_min(1.0)
+    cn = centroids.float().norm(dim=-1)
+    scale = data.float().norm(dim=-1) * 0.5 * (torch.gather(cn, 1, a.long()) + torch.gather(cn, 1, b.long()))
+    return (sa - sb).abs() / scale.clamp_min(1e-20)
+
+
+def check_assignments(got, want, centred, cents, iters, segs):
+    """The parity bar of the module docstring.  Returns the mask of differing assignments."""
+    diff = got != want
+    if iters <= 2:
+        if diff.any():
+            ulp = 2.0 ** -10 if centred.dtype == torch.float16 else 2.0 ** -7
+            tol = 1e-5 if iters == 1 else 2 * ulp
+            margin = tie_margin(centred, last_pass_centroids(centred, cents, iters, segs), got, want)[diff]
+            assert (margin <= tol).all(), f"{int((margin > tol).sum())} of {int(diff.sum())} differing assignments are no ties (worst {float(margin.max()):.3g})"
+    else:
+        assert diff.float().mean() <= DRIFT_ASSIGN, f"{int(diff.sum())} of {diff.numel()} assignments differ"
+    return diff
 
 
 @pytest.mark.parametrize("name", sorted(mg.KMEANS_CASES))
@@ -50,12 +87,9 @@ def test_segment_k_means_against_reference_fixture(name):
             assign[h, members.long()] = c
     assert (assign >= 0).all() and int(sizes.sum()) == heads * tokens
     want = gold["assignments"].to(torch.int32)
-    diff = assign != want
-    assert diff.float().mean() <= 0.01, f"{int(diff.sum())} of {diff.numel()} assignments differ"
-    if diff.any():
-        assert tie_excused(centred, gold["centroids"], assign, want)[diff].float().mean() > 0.5
+    check_assignments(assign, want, centred, cents, iters, segs)
     same = (sizes == gold["sizes"])
-    assert same.float().mean() >= 0.97
+    assert same.float().mean() >= DRIFT_SIZES
     torch.testing.assert_close(cen.float()[same], gold["centroids"].float()[same], rtol=2 ** -9, atol=2e-3)
     torch.testing.assert_close(vsum.float()[same], gold["value_sum"].float()[same], rtol=2 ** -9, atol=2e-2)
 
@@ -66,6 +100,11 @@ BF16_CASES = {
     "ragged_tiles": (3, 1000, 96, 3, 4, 2),
     "many_tiles": (2, 5000, 512, 4, 5, 3),
     "wide": (1, 3000, 1024, 2, 3, 4),
+    "one_iteration": (2, 4000, 256, 4, 1, 5),
+    "two_iterations": (2, 4000, 256, 4, 2, 6),
+    "two_iterations_wide": (1, 6000, 1024, 2, 2, 7),
+    # configuration 0 of the benchmark: 8 kv heads x (8192 - 68) clustered keys, 512 centroids, 10 iterations
+    "cfg0_geometry": (8, 8192 - 68, 512, 1, 10, 0),
 }
 
 
@@ -88,10 +127,7 @@ def test_build_index_against_oracle_bf16(name):
     centred = k - r["mean_key"]
     cen, vsum, clusters, sizes, assign = okm.segment_k_means(centred, v, cents, iters, segs, return_assignments=True)
 
-    diff = r["assign"] != assign
-    assert diff.float().mean() <= 0.01, f"{int(diff.sum())} of {diff.numel()} assignments differ"
-    if diff.any():
-        assert tie_excused(centred, cen, r["assign"], assign)[diff].float().mean() > 0.5
+    diff = check_assignments(r["assign"], assign, centred, cents, iters, segs)
 
     # structure: counts/offsets/order describe r["assign"] exactly, members ascending
     for h in range(heads):
@@ -110,7 +146,7 @@ def test_build_index_against_oracle_bf16(name):
     assert torch.equal(r["cluster_size"].view(torch.int16), r["cluster_count"].to(torch.bfloat16).view(torch.int16))
 
     same = sizes == r["cluster_count"]
-    assert same.float().mean() >= 0.97
+    assert same.float().mean() >= DRIFT_SIZES
     want_cent = cen + r["mean_key"]
     torch.testing.assert_close(r["centroids"].float()[same], want_cent.float()[same], rtol=2 ** -6, atol=2e-2)
     torch.testing.assert_close(r["value_sum"].float()[same], vsum.float()[same], rtol=2 ** -6, atol=6e-2)

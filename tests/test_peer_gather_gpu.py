@@ -64,6 +64,28 @@ def test_two_ranks_on_one_gpu_fill_both_buffers_and_the_wait_returns():
     assert torch.equal(plain.view(torch.int16), outs[0].view(torch.int16))
 
 
+def test_gather_form_beyond_the_single_kernel():
+    """8256 centroids (what configuration 1 has after one re-index of generated tokens): the gather entry point runs
+    the three stage kernels and the attend stage stores the slice into every rank's buffer."""
+    from helpers import gpu_built_layer
+
+    layers, _, q = gpu_built_layer(1, 2, 4, 8256 * 16, 8256, 1, 148, 1915, seed=12, want_ids=False, n_layers=2)
+    g_, gs = 2, 4
+    out_bufs = [torch.zeros((2, g_, gs, 128), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    flag_bufs = [torch.zeros((2,), dtype=torch.int32, device="cuda") for _ in range(2)]
+    epoch = torch.ones((1,), dtype=torch.int32, device="cuda")
+    error = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    keep = []
+    gathers = [make_gather(r, 2, out_bufs, flag_bufs, epoch, error, 3000, keep) for r in range(2)]
+    outs = [layers[r].compute(q, gather=gathers[r]).clone() for r in range(2)]
+    plain = layers[0].compute(q).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(plain.view(torch.int16), outs[0].view(torch.int16))
+    for buf in out_bufs:
+        for r in range(2):
+            assert torch.equal(buf[r].view(torch.int16), outs[r].reshape(g_, gs, 128).view(torch.int16))
+
+
 def test_wait_gives_up_after_its_limit_and_reports_it():
     flags = torch.zeros((2,), dtype=torch.int32, device="cuda")        # only this rank's own flag is ever raised
     mine = torch.zeros((2,), dtype=torch.int32, device="cuda")

@@ -18,13 +18,16 @@ pytestmark = pytest.mark.gpu
 THRESHOLD = 1024
 
 
-@pytest.mark.parametrize("kv_on_host", [False, True], ids=["hbm_tier", "host_tier"])
-def test_reindex_after_1024_generated_tokens(kv_on_host):
+# (kv_on_host, batch, kv_heads): the single-group case is the one where the steady-zone slice handed to the
+# clustering is contiguous in memory (it must still be a copy: the local window is moved over its first rows)
+@pytest.mark.parametrize("kv_on_host,batch,kv_heads", [(False, 2, 2), (True, 2, 2), (False, 1, 1)],
+                         ids=["hbm_tier", "host_tier", "hbm_tier_single_group"])
+def test_reindex_after_1024_generated_tokens(kv_on_host, batch, kv_heads):
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
-    batch, layers, kv_heads, q_heads, seq_len = 2, 2, 2, 8, 1024 + 68
+    layers, q_heads, seq_len = 2, 4 * kv_heads, 1024 + 68
     max_new = THRESHOLD + 16
-    valid_start = [0, 21]
+    valid_start = [0, 21][:batch]
     cfg = generate_config(seq_len, 0.05, 0.2, n_segments=1)
     mapping = {str(l): "cuda:0" for l in range(layers)}
     cache = retroinfer_cache(valid_start, layers, batch, seq_len + max_new, kv_heads, q_heads, 128, torch.bfloat16,

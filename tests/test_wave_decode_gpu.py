@@ -4,8 +4,6 @@ CPU oracle on the same seeded inputs.
 Bars: centroid scores within fp32 accumulation noise; distance keys and selected sets bit-exact
 except where distances tie within 1e-3 of the cut; attention output max-abs <= 2e-2 and
 mean-abs <= 2e-3 against the oracle's fp32 evaluation."""
-import os
-
 import pytest
 import torch
 
@@ -58,11 +56,12 @@ def test_fused_decode_matches_oracle(name, mode):
         out = layer.compute(q.cuda())
     else:   # no (or too little) room for estimation entries in shared memory: the kernel falls back to its
         # global lists — with 16 entries some CTAs have already started copies for the shared-memory form
-        os.environ["RI_WAVE_LOCAL_CAP"] = "0" if mode == "single_kernel_global_lists" else "16"
+        from retrievalattention_b200 import _lib
+        _lib.lib.ri_wave_test_local_cap(0 if mode == "single_kernel_global_lists" else 16)
         try:
             out = layer.compute(q.cuda())
         finally:
-            del os.environ["RI_WAVE_LOCAL_CAP"]
+            _lib.lib.ri_wave_test_local_cap(-1)
     torch.cuda.synchronize()
     v = layer.views()
 

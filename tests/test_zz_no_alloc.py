@@ -32,6 +32,26 @@ def test_static_scratch_matches_caller_scratch_twice():
         assert torch.equal(got.view(torch.int16), expect.view(torch.int16))
 
 
+def test_static_scratch_three_stage_geometry_on_a_used_array():
+    """More than 8192 centroids: the entry point runs the three stage kernels, whose intermediate results all go
+    through the scratch.  Run right after a call of another geometry, so that the built-in array holds that
+    call's leftovers; the result must equal the caller-scratch path to the bit."""
+    from helpers import gpu_built_layer
+
+    small = Case(1, 2, 4, 1024 + 68, 64, 1, 4, 15, seed=23)
+    small_layer = to_gpu_layer(small, build_cpu_index(small), SINK + RECENT)
+    (layer,), _, q = gpu_built_layer(1, 1, 4, 8256 * 16, 8256, 1, 148, 1915, seed=24)
+    assert layer.shape.scratch_bytes() <= 16 << 20
+    for call in range(2):
+        small_layer.compute_static(queries(small, seed=40 + call).cuda())      # dirties the shared array
+        expect = layer.compute(q).clone()
+        got = layer.compute_static(q).clone()
+        torch.cuda.synchronize()
+        err = (got.float() - expect.float()).abs()
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3
+        assert torch.equal(got.view(torch.int16), expect.view(torch.int16))
+
+
 def test_static_scratch_ignores_caller_scratch_pointer():
     case = Case(1, 2, 4, 1024 + 68, 64, 1, 4, 15, seed=22)
     cpu = build_cpu_index(case)
