@@ -54,14 +54,15 @@ METRIC = "decode tok/s at 128K ctx (Llama-3-8B geometry); attn kernel HBM GB/s v
 class Workload:
     """One rank's resident state: the cache of every layer and the per-step inputs."""
 
-    def __init__(self, geo, device, total_steps, kmeans_iters=10, rank=0, log=None, world=1):
+    def __init__(self, geo, device, total_steps, kmeans_iters=10, rank=0, log=None, world=1, weak=True):
         from retrievalattention_b200.cache_hub import retroinfer_cache
         from retrievalattention_b200.head_shard import HeadGather, HeadShard
 
-        # N ranks: global batch = batch * N requests, KV heads sharded over the ranks (then batch), so
-        # every rank holds the same number of (request, kv-head) groups as the 1-GPU workload.
+        # N ranks, weak scaling: global batch = batch * N requests, KV heads sharded over the ranks (then batch), so
+        # every rank holds the same number of (request, kv-head) groups as the 1-GPU workload.  Not weak: the
+        # geometry's own batch, so a rank's share shrinks with N.
         self.global_geo = geo
-        self.shard = HeadShard(rank, world, geo.kv_heads, geo.q_heads, geo.batch * world)
+        self.shard = HeadShard(rank, world, geo.kv_heads, geo.q_heads, geo.batch * (world if weak else 1))
         geo = replace(geo, kv_heads=self.shard.local_kv_heads, q_heads=self.shard.local_q_heads,
                       batch=self.shard.local_batch)
         self.gather = HeadGather(self.shard, HeadGather.make_groups(self.shard)) if world > 1 else None
@@ -107,16 +108,12 @@ class Workload:
         self.peer = None
         if self.gather is not None:
             # the gather of the head slices: done by the decode kernel itself through peer-mapped buffers
-            # (PeerGather); RI_GATHER=nccl, or a failed set-up of those buffers, selects the NCCL all-gather
+            # (PeerGather); a failed set-up of those buffers is an error.  The NCCL all-gather is opt-in only
+            # (RI_GATHER=nccl): there is no silent change of the exchange under a measurement.
             if os.environ.get("RI_GATHER", "peer") != "nccl":
-                try:
-                    from retrievalattention_b200.head_shard import PeerGather
-                    self.peer = PeerGather(self.shard, geo.layers, geo.batch, geo.q_heads, geo.head_dim, torch.bfloat16,
-                                           device, group=self.gather.group)
-                except Exception as exc:     # noqa: BLE001 — any set-up failure falls back to the collective
-                    self.peer_error = repr(exc)[:200]
-                    if log:
-                        log("peer-store gather unavailable, using NCCL: " + self.peer_error)
+                from retrievalattention_b200.head_shard import PeerGather
+                self.peer = PeerGather(self.shard, geo.layers, geo.batch, geo.q_heads, geo.head_dim, torch.bfloat16,
+                                       device, group=self.gather.group)
             if self.peer is None:
                 self.gathered = torch.zeros((geo.layers, self.shard.head_shards) + tuple(shp_q[2:]),
                                             dtype=torch.bfloat16, device=device)
@@ -147,8 +144,8 @@ class Workload:
             with torch.cuda.graph(graph):
                 self.step_body()
             self.graph = graph
-        except Exception as exc:             # e.g. a collective that cannot be captured: step eagerly
-            if self.gather is None:
+        except Exception as exc:             # an NCCL collective that cannot be captured (RI_GATHER=nccl): step eagerly
+            if self.gather is None or self.peer is not None:
                 raise
             self.graph = None
             self.capture_error = repr(exc)[:200]
@@ -332,6 +329,58 @@ def layer_parity(wl, layer_idx, step):
     return parity, sec
 
 
+def reference_gpu_sequence(wl, steps):
+    """The reference's OWN CUDA kernels on the same GPU and the same layers: the part of its ``compute`` that its
+    shipped extension modules cover — ``batch_gemm_softmax`` (CUTLASS GEMM + softmax), the group sum, the mask,
+    ``torch.topk`` of max_compute clusters and ``gather_copy_vectors`` of the estimation rows
+    (cache_hub/retroinfer_cache.py:569-575, :601-605) — compiled for sm_100a into ``oracle/_ref``.  Its two
+    ``weighted_flash_decoding`` calls come from a package that is not available, and its host wave buffer is left
+    out, so this is a LOWER bound of the reference's per-layer GPU time.  Times all layers from one CUDA graph;
+    returns None when the modules were never built."""
+    from oracle import build_ref
+
+    gs_mod, cp_mod = build_ref.load("gemm_softmax"), build_ref.load("Copy")
+    if gs_mod is None or cp_mod is None:
+        return None
+    c, s, dev = wl.cache, wl.shape, wl.device
+    g, gsz, n_c, d = s.groups, s.group_size, s.n_centroids, 128
+    k_all = s.nprobe + s.n_estimate
+    gemm_o = torch.zeros((g, gsz, n_c), dtype=torch.bfloat16, device=dev)
+    softmax_o = torch.zeros_like(gemm_o)
+    blocks = (n_c + 255) // 256
+    norm = torch.zeros((g, gsz, blocks), dtype=torch.float32, device=dev)
+    ssum = torch.zeros_like(norm)
+    es_c = torch.zeros((g, s.n_estimate, d), dtype=torch.bfloat16, device=dev)
+    es_v = torch.zeros_like(es_c)
+    es_s = torch.zeros((g, s.n_estimate), dtype=torch.bfloat16, device=dev)
+    dtype_min = torch.finfo(torch.bfloat16).min
+
+    def body():
+        for l in range(len(c.centroids)):
+            q = wl.q_in[l].view(g, gsz, d)
+            gs_mod.batch_gemm_softmax(q, c.centroids[l], gemm_o, norm, ssum, softmax_o, g, gsz, n_c, d, 1 / 128 ** 0.5, 0)
+            dist = torch.sum(softmax_o, dim=1)
+            dist.masked_fill_(c.centroids_mask[l], dtype_min)
+            ci = torch.topk(dist, k_all, dim=-1, largest=True, sorted=True)[1]
+            cp_mod.gather_copy_vectors(c.centroids[l], es_c, c.value_sum[l], es_v, c.cluster_size[l], es_s, ci, g, n_c,
+                                       s.n_estimate, k_all, s.nprobe, s.n_estimate)
+
+    # the reference's GEMM is issued on the legacy default stream (batch_gemm_softmax.h:520), which cannot be captured
+    # in a graph: time eager launches on the default stream, launch gaps included (as the reference itself runs)
+    body()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        body()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (steps * len(c.centroids))
+    return {"sequence": "reference kernels built for sm_100a: batch_gemm_softmax + sum + masked_fill + topk + gather_copy_vectors "
+                        "(scores, selection, estimation gather; its attention calls are not available)",
+            "ms_per_layer": round(ms, 4), "launch": "eager on the default stream, as the reference issues it"}
+
+
 def model_decode(wl, geo, args, warm, log):
     """Decode tokens/s of the whole model step around the same caches: embedding,
     per layer RMS norm -> fused QKV projection -> rotary embedding -> cache update + wave-index
@@ -390,32 +439,11 @@ def model_decode(wl, geo, args, warm, log):
             "note": "per layer: 3 of this library's element-wise kernels + the decode kernel + 4 library GEMMs"}
 
 
-# ----------------------------------------------------------------------------------------------
-# decode benchmark
-# ----------------------------------------------------------------------------------------------
-def run_decode(geo, args, rank, world, local_rank, log):
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN"):
-            os.environ["NCCL_DEBUG"] = "ERROR"     # keep NCCL's banner off stdout: one JSON line only
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
-        # Host-side barriers and the max-over-ranks reduction go over gloo, so that no eager NCCL collective
-        # is ever issued on a communicator that also carries graph-captured work.
-        cpu_group = dist.new_group(backend="gloo")
-
-    warm = max(args.warmup, 3)
-    stage_steps = min(args.steps, 4)
-    total = 2 * (warm + args.steps) + stage_steps + 2
-    with_model = world == 1 and not args.no_model
-    if with_model:
-        total += 2 * (warm + args.steps) + 2      # the model run appends to the same steady zones
-    wl = Workload(geo, device, total, args.kmeans_iters, rank, log, world)
-    wl.capture()      # consumes 2 steps of the steady zone
-
+def measure_steps(wl, args, warm, rank, world, local_rank, dist, cpu_group):
+    """Times ``args.steps`` decode steps twice — inputs resident in HBM (one graph replay per step), then end to
+    end with q/k/v starting in pinned host memory and the outputs ending there — each after ``warm`` untimed
+    steps, between barriers, with CUDA events; several ranks: the maximum over the ranks.  Returns
+    (ms resident, ms end to end, clock record of rank 0, result of the gather check)."""
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
@@ -426,10 +454,9 @@ def run_decode(geo, args, rank, world, local_rank, log):
             wl.q_in.copy_(wl.q_all[st]); wl.k_in.copy_(wl.k_all[st]); wl.v_in.copy_(wl.v_all[st])
             wl.replay()
 
-    # ---- `value`: inputs resident in HBM, one graph replay per step ----
     run_resident(0, warm)
     barrier()
-    sampler = ClockSampler(local_rank)     # samples over both timed regions (value and e2e)
+    sampler = ClockSampler(local_rank)     # samples over both timed regions
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -439,7 +466,6 @@ def run_decode(geo, args, rank, world, local_rank, log):
     barrier()
     ms = e0.elapsed_time(e1)
 
-    # ---- `e2e`: q/k/v start in pinned host memory, outputs end there ----
     base = warm + args.steps
     q_host, k_host, v_host = (t.cpu().pin_memory() for t in (wl.q_all, wl.k_all, wl.v_all))
     out_host = torch.empty(wl.out.shape, dtype=wl.out.dtype).pin_memory()
@@ -481,12 +507,38 @@ def run_decode(geo, args, rank, world, local_rank, log):
             flags = torch.tensor([1.0 if ok else 0.0])
             dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=cpu_group)
             gather_check = "ok" if flags.item() == 1.0 else "MISMATCH"
+    return ms, ms_e2e, clocks, gather_check
+
+
+# ----------------------------------------------------------------------------------------------
+# decode benchmark
+# ----------------------------------------------------------------------------------------------
+def run_decode(geo, args, rank, world, local_rank, log):
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist, cpu_group = None, None
+    if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN"):
+            os.environ["NCCL_DEBUG"] = "ERROR"     # keep NCCL's banner off stdout: one JSON line only
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+        # Host-side barriers and the max-over-ranks reduction go over gloo, so that no eager NCCL collective
+        # is ever issued on a communicator that also carries graph-captured work.
+        cpu_group = dist.new_group(backend="gloo")
+
+    warm = max(args.warmup, 3)
+    stage_steps = min(args.steps, 4)
+    total = 2 * (warm + args.steps) + stage_steps + 2
+    with_model = world == 1 and not args.no_model
+    if with_model:
+        total += 2 * (warm + args.steps) + 2      # the model run appends to the same steady zones
+    wl = Workload(geo, device, total, args.kmeans_iters, rank, log, world)
+    wl.capture()      # consumes 2 steps of the steady zone
+    ms, ms_e2e, clocks, gather_check = measure_steps(wl, args, warm, rank, world, local_rank, dist, cpu_group)
 
     # ---- per-kernel time and roofline (separate eager pass, events around each launch) ----
     stage_ms, n_ret_rows, static_len = time_stages(wl, 2 * (warm + args.steps), stage_steps)
-    if rank != 0:
-        dist.barrier(group=cpu_group)  # rank 0 is still timing the CPU baseline
-        return
     peak, _, peak_kind = measured_peaks()
     alg = algorithmic_bytes(wl, n_ret_rows, static_len)
     # the library's switch to the three-kernel form, which it also takes beyond 8192 centroids
@@ -551,7 +603,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                     f"with host token ids, {gbs:.0f} GB/s = {gbs / peak:.3f} of peak")
         else:
             cfgd["decode_model"] = dm.get("unavailable", "unavailable")
-    if not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline:
         parity, sec = layer_parity(wl, 0, warm)
         result["parity"] = parity
         cfgd["parity"] = (f"layer 0, {geo.groups} groups vs CPU oracle: " + ("ok" if parity["ok"] else "FAILED")
@@ -561,14 +613,68 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                   "cores": os.cpu_count(), "kind": "port",
                                   "sample": f"layer 0 of the same workload, all {geo.groups} groups, median of 2 runs "
                                             f"({sec * 1e3:.1f} ms), scaled by {geo.layers} layers"}
+    if world == 1 and not args.no_cpu_baseline:
+        rg = reference_gpu_sequence(wl, min(args.steps, 8))
+        if rg is not None:
+            ours = stage_ms["scan"] + stage_ms["select"]
+            rg["this_library_scan_plus_select_ms_per_layer"] = round(ours, 4)
+            result["reference_gpu"] = rg
+            cfgd["reference_gpu"] = (f"reference's own kernels (scores+softmax, topk, estimation gather): {rg['ms_per_layer'] * 1e3:.1f} us "
+                                     f"per layer; same work here (scan + select stage kernels): {ours * 1e3:.1f} us; whole layer "
+                                     f"here (single kernel, attention included): {stage_ms['decode'] * 1e3:.1f} us")
     if world == 1 and not args.no_kmeans and args.config == "cfg1":
         km = kmeans_summary(GEOMETRIES["cfg2"], args, log)
         result["kmeans"] = km
         cfgd["kmeans"] = (f"cfg2 build {km['ms']} ms, {km['tflops']} TFLOP/s = {km['frac']} of sustained bf16 peak "
                           f"({km['frac_of_burst_peak']} of burst)")
-    print(json.dumps(result), flush=True)
+    if world > 1 and not args.no_cfg4 and args.config == "cfg1":
+        # configuration 4 (Qwen2.5-72B geometry, KV heads sharded over the ranks, batch 16) on the same ranks
+        wl.graph = wl.cache = wl.peer = wl.gather = None
+        del wl
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        c4 = run_cfg4(args, rank, world, local_rank, device, dist, cpu_group, log)
+        result["cfg4"] = c4
+        cfgd["cfg4"] = (f"{c4['layers']} of 80 layers: {c4['ms_per_step']} ms/step, {c4['tok_s']} tok/s "
+                        f"({c4['tok_s_at_80_layers']} at 80 layers), e2e {c4['e2e_tok_s']}, gather {c4['gather_check']}")
+    if rank == 0:
+        print(json.dumps(result), flush=True)
     if world > 1:
         dist.barrier(group=cpu_group)
+
+
+def run_cfg4(args, rank, world, local_rank, device, dist, cpu_group, log):
+    """Configuration 4 on the ranks of this run: 64 q / 8 kv heads (gs 8), batch 16, context 131072, the KV heads
+    sharded over the ranks (8 ranks: one head each), the head slices gathered by the decode kernel's peer stores.
+    As many of the 80 layers as fit beside the allocator's leftovers (all 80 at 8 ranks)."""
+    from retrievalattention_b200.head_shard import HeadShard
+
+    geo = GEOMETRIES["cfg4"]
+    shard = HeadShard(rank, world, geo.kv_heads, geo.q_heads, geo.batch)
+    cfg = geo.index()
+    groups = shard.local_kv_heads * shard.local_batch
+    per_layer = groups * ((geo.context - SINK - RECENT) * 512 + cfg.n_centroids * (512 + 16) + 4096 * 512)
+    free = torch.cuda.mem_get_info(device)[0]
+    layers = torch.tensor([min(geo.layers, int((free - (20 << 30)) // per_layer))])
+    dist.all_reduce(layers, op=dist.ReduceOp.MIN, group=cpu_group)
+    layers = max(int(layers.item()), 1)
+    steps, warm = min(args.steps, 16), 3
+    sub = argparse.Namespace(**{**vars(args), "steps": steps})
+    wl = Workload(replace(geo, layers=layers), device, 2 * (warm + steps) + 4, args.kmeans_iters, rank, log, world, weak=False)
+    wl.capture()
+    ms, ms_e2e, _, gather_check = measure_steps(wl, sub, warm, rank, world, local_rank, dist, cpu_group)
+    ms_step = ms / steps
+    out = {"workload": f"{geo.name}: {geo.q_heads}q/{geo.kv_heads}kv heads, batch {geo.batch}, ctx {geo.context}, "
+                       f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; per rank {shard.local_kv_heads} kv heads x batch "
+                       f"{shard.local_batch} = {groups} groups, gs {geo.q_heads // geo.kv_heads}",
+           "layers": layers, "steps": steps, "ms_per_step": round(ms_step, 4), "ms_per_layer": round(ms_step / layers, 5),
+           "tok_s": round(geo.batch / ms_step * 1e3, 1),
+           "tok_s_at_80_layers": round(geo.batch / (ms_step / layers * geo.layers) * 1e3, 1),
+           "e2e_tok_s": round(geo.batch * steps / ms_e2e * 1e3, 1), "gather_check": gather_check,
+           "scaling": "strong (batch 16 fixed, a rank's share of the heads shrinks with the ranks)"}
+    wl.graph = wl.cache = wl.peer = None
+    return out
 
 
 def reference_arm(geo, args, log):
@@ -707,6 +813,8 @@ def main():
                     help="skip the whole-model decode step (projections, MLP, vocabulary head with random weights around "
                          "the same caches; key decode_model, single GPU)")
     ap.add_argument("--no-kmeans", action="store_true", help="skip the short clustering run (key kmeans, single GPU)")
+    ap.add_argument("--no-cfg4", action="store_true",
+                    help="several GPUs: skip the run of configuration 4 (72B geometry, heads sharded) after the main one")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
     args = ap.parse_args()
 

@@ -97,7 +97,9 @@ constexpr float RI_LOG2E = 1.4426950408889634f;
 // Measured on B200: worth a few tenths of a microsecond per launch for scan and select (ids 0, 1,
 // on by default).  The attend kernel (id 2: 8-CTA clusters with ~100 KB of shared memory each)
 // got slower when its CTAs became resident early, so it and the steady append (id 4) are
-// launched in plain stream order.
+// launched in plain stream order.  The single decode kernel (id 5) and the gather wait (id 6) are
+// on: on one GPU it makes no difference to the decode kernel, between several GPUs the wait
+// kernel's launch hides behind the decode kernel and the next decode kernel's behind the wait.
 __device__ __forceinline__ void ri_pdl_enter() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -114,7 +116,7 @@ inline cudaError_t ri_launch_pdl_id(int id, void (*kernel)(KArgs...), dim3 grid,
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  static const int mask = getenv("RI_PDL_MASK") ? atoi(getenv("RI_PDL_MASK")) : 3;   // per-kernel switch (debugging)
+  static const int mask = getenv("RI_PDL_MASK") ? atoi(getenv("RI_PDL_MASK")) : 0x63;   // per-kernel switch
   cfg.attrs = attr;
   cfg.numAttrs = (mask >> id) & 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);

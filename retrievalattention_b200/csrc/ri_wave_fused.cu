@@ -31,9 +31,14 @@ template <int CL>
 struct Geom {
   static constexpr int kMaxSlice = kFusedMaxCentroids / CL;          // centroids a CTA's slice holds at most
   static constexpr int kKeys = kMaxSlice / kFusedThreads;            // keys per thread: 8 (CL 4) or 4 (CL 8)
-  static constexpr int kScoreStride = kMaxSlice + 8;                 // floats per head in shared memory (bank spread)
+  // floats per head in shared memory: four words of padding after every 32 (see score_at), eight more between heads
+  static constexpr int kScoreStride = kMaxSlice + kMaxSlice / 8 + 8;
   static_assert(kKeys == 4 || kKeys == 8, "a thread's keys are loaded as one or two 16-byte pieces");
 };
+
+// Place of centroid e of the slice in a head's row of scores: a thread of the selection owns a run of 4 or 8
+// consecutive centroids, so without the padding its lanes would sit 8 words apart and collide on 4 banks.
+__device__ __forceinline__ int score_at(int e) { return e + ((e >> 5) << 2); }
 
 struct FusedArgs {
   SelectArgs sel;
@@ -129,7 +134,7 @@ __device__ __forceinline__ void scan_slice(const FusedArgs& f, int g, int lo, in
       const float v0 = f.alpha * acc[0], v1 = f.alpha * acc[1];
       const bool ok = r < gs && c0 < hi;               // slices are multiples of 8: a tile is entirely in or out
       if (ok) {
-        *reinterpret_cast<float2*>(s_sc + r * kScoreStride + (c0 - lo)) = make_float2(v0, v1);
+        *reinterpret_cast<float2*>(s_sc + r * kScoreStride + score_at(c0 - lo)) = make_float2(v0, v1);
         if (f.views) *reinterpret_cast<float2*>(f.scores + ((int64_t)g * gs + r) * C + c0) = make_float2(v0, v1);
       }
       rv[j][0] = ok ? Elem<DT>::round(v0) : -INFINITY;
@@ -280,7 +285,7 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       if (h < gs) {
 #pragma unroll
         for (int q4 = 0; q4 < KEYS / 4; ++q4) {
-          const float4 s4 = *reinterpret_cast<const float4*>(s_sc + h * kScoreStride + e0 + 4 * q4);
+          const float4 s4 = *reinterpret_cast<const float4*>(s_sc + h * kScoreStride + score_at(e0 + 4 * q4));
           const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i)
@@ -396,12 +401,9 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
       } else if (inK) {
         est_mask |= 1u << i;
         const int lpos = est_lp[i];
-        if (lpos < f.cap) {
+        if (lpos < f.cap) {      // the scores follow below, one entry per thread
           est_idx[lpos] = (uint16_t)(e0 + i);
           est_wt[lpos] = Elem<DT>::from_bits((uint16_t)(tc.szw[i >> 1] >> (16 * (i & 1))));
-#pragma unroll
-          for (int h = 0; h < kMaxHeads; ++h)
-            if (h < gs) est_sc[h * f.cap + lpos] = s_sc[h * kScoreStride + e0 + i] * RI_LOG2E;
         }
       }
       gtK += key[i] > TK; eqK += key[i] == TK; gtP += key[i] > TP; eqP += key[i] == TP;
@@ -412,6 +414,14 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
   if (tid == 0) {
     s_pub[0] = my_ret;
     s_pub[1] = my_est;
+  }
+  __syncthreads();
+  // log2-domain scores of the estimation entries, entry by entry (uniform work, consecutive stores)
+  for (int j = tid; j < min(my_est, f.cap); j += T) {
+    const int e = score_at((int)est_idx[j]);
+#pragma unroll
+    for (int h = 0; h < kMaxHeads; ++h)
+      if (h < gs) est_sc[h * f.cap + j] = s_sc[h * kScoreStride + e] * RI_LOG2E;
   }
   __syncthreads();
   cluster.sync();       // every CTA's candidate list, estimation list and counts are complete
@@ -602,7 +612,7 @@ __device__ __forceinline__ bool select_in_cluster(const FusedArgs& f, int g, int
             a.est_w[(int64_t)g * a.e_pad + pe] = Elem<DT>::from_bits((uint16_t)(tc.szw[i >> 1] >> (16 * (i & 1))));
 #pragma unroll
             for (int h = 0; h < kMaxHeads; ++h)
-              if (h < gs) a.est_s2[((int64_t)g * kMaxHeads + h) * a.e_pad + pe] = s_sc[h * kScoreStride + e0 + i] * RI_LOG2E;
+              if (h < gs) a.est_s2[((int64_t)g * kMaxHeads + h) * a.e_pad + pe] = s_sc[h * kScoreStride + score_at(e0 + i)] * RI_LOG2E;
             if (a.estimated_ids) a.estimated_ids[(int64_t)g * a.E + pe] = lo + e0 + i;
           }
         }

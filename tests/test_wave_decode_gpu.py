@@ -22,6 +22,9 @@ CASES = {
     "tight_budget": Case(1, 2, 4, 2048 + 68, 64, 1, 8, 14, seed=7, buffer_pages=9),
     "empty_clusters": Case(1, 2, 4, 1024 + 68, 64, 1, 4, 15, seed=8, duplicate_rows=37),
     "cfg0_geometry": Case(1, 8, 4, 8192, 512, 1, 9, 118, seed=0, iters=3),
+    # 19 groups and more: the single kernel runs with 4-CTA clusters (below: 8-CTA clusters)
+    "many_groups_gs8": Case(5, 4, 8, 1024 + 68, 64, 1, 4, 15, seed=9),
+    "many_groups_gs3": Case(7, 3, 3, 1536 + 68, 96, 2, 5, 22, seed=10),
 }
 
 
