@@ -507,6 +507,8 @@ def measure_steps(wl, args, warm, rank, world, local_rank, dist, cpu_group):
             flags = torch.tensor([1.0 if ok else 0.0])
             dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=cpu_group)
             gather_check = "ok" if flags.item() == 1.0 else "MISMATCH"
+            if rank == 0:
+                gather_check += " " + json.dumps(wl.peer.wait_times_us())
     return ms, ms_e2e, clocks, gather_check
 
 
@@ -573,7 +575,7 @@ def run_decode(geo, args, rank, world, local_rank, log):
                    "l2": "inputs larger than L2 (each layer-step touches its own ~110 MB; ~3.5 GB per step)",
                    "index": f"built by ri_kmeans_build during untimed set-up ({args.kmeans_iters} iterations, "
                             f"median {wl.prefill_index_ms:.1f} ms per request-layer incl. layout)",
-                   "gather_check": gather_check,
+                   "gather_check": gather_check,    # "ok" + the flag wait's microseconds per layer on rank 0 (last step)
                    "graph": "one CUDA graph per decode step" if wl.graph is not None else
                             "eager stepping (capture failed: " + getattr(wl, "capture_error", "?") + ")"},
         "e2e": {"value": round(tokens / (ms_e2e / 1e3), 2), "unit": "tok/s",

@@ -112,6 +112,13 @@ int ri_wave_scan(const ri_wave_layer* p, void* stream);    /* q.C^T scores -> sc
 int ri_wave_select(const ri_wave_layer* p, void* stream);  /* softmax, group sum, top-k split */
 int ri_wave_attend(const ri_wave_layer* p, void* stream);  /* weighted split-K flash decoding */
 
+/* Selection made ahead of time with ANOTHER query (the reference's `use_cluster_estimation`, model_hub/LLM.py:102-107 and
+ * cache_hub/retroinfer_cache.py:582-595: the next layer's clusters are searched one layer early with an estimate of
+ * its query): run ri_wave_scan + ri_wave_select with the estimated query on the layer's own scratch; when the real
+ * query arrives, ri_wave_rescore recomputes the estimation entries' scores for it (p->d_q = the real query) and
+ * ri_wave_attend attends the pre-selected clusters. */
+int ri_wave_rescore(const ri_wave_layer* p, void* stream);
+
 /* Host tier: the attend stage over an execution buffer assembled by ri_gather_copy_and_concat
  * (steady zone ++ missed pages from the host list ++ hit pages from the GPU page cache).  The
  * estimation part is as in ri_wave_attend (it uses what ri_wave_select left in the scratch); the
@@ -146,6 +153,8 @@ typedef struct ri_wave_gather {
   const uint32_t* d_flags;         /* local: this layer's flag words, one per rank */
   const uint32_t* d_epoch;         /* local: [1] the current step's epoch */
   int32_t* d_error;                /* local: set to 1 when a wait ran out */
+  unsigned long long* d_stamps;    /* optional (may be NULL), local [3]: the wait kernel's global-timer readings (ns) at
+                                      entry, after this rank's flags are raised, and when the last rank's flag was seen */
 } ri_wave_gather;
 /* ri_wave_decode_layer plus the stores described above (p->d_out is written too).  Geometries beyond the single
  * decode kernel (more than 8192 centroids, e.g. after a re-index of generated tokens) run the three stage

@@ -73,7 +73,7 @@ def surviving_clusters(ranked_ids: torch.Tensor, sizes: torch.Tensor, page_size:
 
 def compute(q, centroids, value_sum, cluster_size_dtype, mask, sizes, offsets, csr_keys, csr_values,
             steady_keys, steady_values, static_len, nprobe, max_compute, page_size, buffer_pages,
-            return_parts=False):
+            return_parts=False, select_q=None):
     """One decode attention step for one layer, cache_hub/retroinfer_cache.py:549-697,
     with every cluster read from the cluster-contiguous store (which is what the
     execution buffer holds after ``gather_copy_and_concat``, :642-648, whether the
@@ -82,12 +82,15 @@ def compute(q, centroids, value_sum, cluster_size_dtype, mask, sizes, offsets, c
     q [B, 1, Hq, d]; centroids/value_sum [G, C, d]; cluster_size_dtype [G, C] (bf16);
     mask [G, C] bool; sizes [G, C] int32; offsets [G, C+1] int32;
     csr_keys/values [G, N, d]; steady_keys/values [G, S_max, d].
+    ``select_q`` (same shape as q): the query the clusters are searched with when it is not the attending query —
+    ``use_cluster_estimation`` searches a layer's clusters one layer early with an estimate of its query (:582-595)
+    and attends them with the real one (:611-617, :666-674).
     Returns out [B, 1, Hq, d] in q.dtype."""
     g, c, d = centroids.shape
     b, _, hq, _ = q.shape
     gs = hq * b // g
     qg = q.reshape(g, gs, d)
-    dist = score_select.cluster_distance(qg, centroids, mask)
+    dist = score_select.cluster_distance(qg if select_q is None else select_q.reshape(g, gs, d), centroids, mask)
     ret_ids, est_ids = score_select.select_clusters(dist, nprobe, max_compute)
     e = est_ids.shape[1]
     out = torch.empty((g, 1, gs, d), dtype=q.dtype)

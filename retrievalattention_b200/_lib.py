@@ -40,7 +40,7 @@ class WaveGather(C.Structure):
     _fields_ = [
         ("n_ranks", C.c_int32), ("rank", C.c_int32), ("wait_limit_us", C.c_int32), ("reserved", C.c_int32),
         ("d_out_slots", C.c_void_p), ("d_flag_slots", C.c_void_p), ("d_flags", C.c_void_p),
-        ("d_epoch", C.c_void_p), ("d_error", C.c_void_p),
+        ("d_epoch", C.c_void_p), ("d_error", C.c_void_p), ("d_stamps", C.c_void_p),
     ]
 
 
@@ -73,7 +73,7 @@ def _load() -> C.CDLL:
     lib.ri_wave_scratch_bytes.restype = C.c_int64
     lib.ri_wave_scratch_bytes.argtypes = [C.POINTER(WaveLayer)]
     for name in ("ri_wave_decode_layer", "ri_wave_decode_layer_static", "ri_wave_scan", "ri_wave_select",
-                 "ri_wave_attend"):
+                 "ri_wave_attend", "ri_wave_rescore"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(WaveLayer), C.c_void_p]

@@ -23,7 +23,14 @@ offload, no CPU re-layout).  Two storage tiers:
 After every 1024 generated tokens ``decode_update_kv_cache`` folds them into the index (``_update_kv_cache``,
 :462-524), provided ``max_new_length`` announced that many at construction.
 
-``use_cluster_estimation`` is accepted for compatibility and ignored.
+``use_cluster_estimation=True`` (HBM tier): ``compute(queries, l, queries_next)`` also searches layer ``l + 1``'s
+clusters with ``queries_next`` (the caller's estimate of the next layer's query, model_hub/LLM.py:102-107), and a
+layer whose clusters were searched ahead in this step attends those clusters with its real query instead of
+searching again (:565, :582-595).  Layers without a search made for them (the first ones, or whenever the caller
+passes no ``queries_next``) search with their own query — the reference instead reuses whatever an earlier step
+left in its index buffer for layer 2, an off-by-one that is not reproduced.  The point of the feature in the
+reference is to start the host wave buffer's work one layer early; with the cluster store in HBM there is nothing
+to hide, so this mode exists for its results (it is slower than the single kernel: five launches per layer).
 """
 from __future__ import annotations
 
@@ -54,7 +61,7 @@ class retroinfer_cache(KV_Cache):
         # decode kernel of the following compute() stores them into the steady zone itself (one launch less per
         # layer).  The two calls always come in pairs (attn_hub.retroinfer_decode_attn); the rows passed must stay
         # unchanged until that compute().  HBM tier only.
-        self.fuse_append = bool(fuse_append) and not kv_on_host
+        self.fuse_append = bool(fuse_append) and not kv_on_host and not use_cluster_estimation
         self.static_pattern_start = static_pattern_start
         self.static_pattern_end = static_pattern_end
         self.static_pattern_total = static_pattern_start + static_pattern_end
@@ -122,6 +129,13 @@ class retroinfer_cache(KV_Cache):
                 "append_pos": torch.tensor([self.static_pattern_total], dtype=torch.int32, device=dev),
             }
         self._layers = [None] * layer_num
+        # use_cluster_estimation: a search made one layer ahead lives in the layer's own scratch until it is used
+        self._ahead = [False] * layer_num
+        if self.use_cluster_estimation:
+            if kv_on_host:
+                raise NotImplementedError("use_cluster_estimation is built for the HBM tier (kv_on_host=False)")
+            for dev in self._per_device:
+                self._per_device[dev]["layer_scratch"] = {}
         if self.kv_on_host:
             self._init_host_tier(cache_cluster_num)
 
@@ -232,7 +246,18 @@ class retroinfer_cache(KV_Cache):
                 want_ids=self.kv_on_host, host_tier=self.kv_on_host,
                 steady_keys=self.steady_zone_keys[ldx].view(g, self.static_stride, self.head_dim),
                 steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
-                static_len=per["static_len"], scratch=per["scratch"])
+                static_len=per["static_len"], scratch=self._scratch_for(ldx, per))
+
+    def _scratch_for(self, ldx, per):
+        """One scratch per device; with ``use_cluster_estimation`` one per layer (a search made ahead must survive
+        the other layers' work)."""
+        if not self.use_cluster_estimation:
+            return per["scratch"]
+        need = self.shape.scratch_bytes()
+        old = per["layer_scratch"].get(ldx)
+        if old is None or old.numel() < need:
+            per["layer_scratch"][ldx] = wave.new_scratch(self.shape, per["static_len"].device)
+        return per["layer_scratch"][ldx]
 
     # ------------------------------------------------------------------ re-index
     def _update_kv_cache(self):
@@ -325,6 +350,10 @@ class retroinfer_cache(KV_Cache):
             if gather is not None:
                 raise NotImplementedError("the peer-store gather is built for the HBM tier only")
             out = self._compute_host_tier(queries.contiguous(), layer_idx, out)
+        elif self.use_cluster_estimation:
+            if gather is not None:
+                raise NotImplementedError("the peer-store gather is not combined with use_cluster_estimation")
+            out = self._compute_with_estimation(queries.contiguous(), layer_idx, queries_next, out)
         else:
             out = self._layers[layer_idx].compute(queries.contiguous(), out,
                                                   gather=None if gather is None else gather.params[layer_idx])
@@ -333,6 +362,28 @@ class retroinfer_cache(KV_Cache):
             for p in self._per_device.values():
                 p["static_len"].add_(1)
         return out.view(self.batch_size, 1, self.num_heads, self.head_dim)
+
+    def _compute_with_estimation(self, queries, layer_idx, queries_next, out):
+        """``use_cluster_estimation`` (:565, :582-595): attend the clusters searched one layer ahead if there are
+        any, else search now; then search the next layer's clusters with ``queries_next``."""
+        layer = self._layers[layer_idx]
+        if out is None:
+            out = torch.empty_like(queries)
+        if self._ahead[layer_idx]:
+            self._ahead[layer_idx] = False
+            layer.stage("rescore", queries, out)      # the estimation entries' scores for the real query
+            layer.stage("attend", queries, out)
+        else:
+            layer.compute(queries, out)
+        if queries_next is not None and layer_idx + 1 < self.layer_num:
+            nxt = self._layers[layer_idx + 1]
+            q_next = queries_next.contiguous()
+            self._q_next_alive = q_next
+            sink = torch.empty_like(q_next)           # the stages take an output pointer; scan and select do not write it
+            nxt.stage("scan", q_next, sink)
+            nxt.stage("select", q_next, sink)
+            self._ahead[layer_idx + 1] = True
+        return out
 
     def _compute_host_tier(self, queries, layer_idx, out):
         """One layer with the cluster store in pinned host memory (the reference's steps 1-10,

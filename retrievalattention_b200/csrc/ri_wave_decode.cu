@@ -53,7 +53,52 @@ __global__ void steady_append_kernel(const uint4* __restrict__ k, const uint4* _
   sv[((int64_t)g * stride + p) * 16 + c] = v[i];
 }
 
+// Scores of the estimation entries that are in the scratch, recomputed for ANOTHER query: one warp per entry, fp32 dot
+// products of the entry's centroid with the group's query heads, stored in the log2 domain where the attend stage
+// expects them.
+template <int DT>
+__global__ void __launch_bounds__(256) wave_rescore_kernel(const uint2* __restrict__ q, const uint2* __restrict__ cent,
+                                                           const int32_t* __restrict__ est_ids, float* __restrict__ est_s2,
+                                                           int C, int gs, int E, int e_pad, float scale2) {
+  const int g = blockIdx.y, lane = threadIdx.x & 31, i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= E) return;
+  const int c = min(max(est_ids[(int64_t)g * e_pad + i], 0), C - 1);
+  const uint2 cw = cent[((int64_t)g * C + c) * 32 + lane];         // this lane's four channels
+  const float c0 = Elem<DT>::from_bits((uint16_t)(cw.x & 0xffffu)), c1 = Elem<DT>::from_bits((uint16_t)(cw.x >> 16));
+  const float c2 = Elem<DT>::from_bits((uint16_t)(cw.y & 0xffffu)), c3 = Elem<DT>::from_bits((uint16_t)(cw.y >> 16));
+  for (int h = 0; h < gs; ++h) {
+    const uint2 qw = q[((int64_t)g * gs + h) * 32 + lane];
+    float s = c0 * Elem<DT>::from_bits((uint16_t)(qw.x & 0xffffu)) + c1 * Elem<DT>::from_bits((uint16_t)(qw.x >> 16)) +
+              c2 * Elem<DT>::from_bits((uint16_t)(qw.y & 0xffffu)) + c3 * Elem<DT>::from_bits((uint16_t)(qw.y >> 16));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) est_s2[((int64_t)g * kMaxHeads + h) * e_pad + i] = s * scale2;
+  }
+}
+
 }  // namespace
+
+extern "C" int ri_wave_rescore(const ri_wave_layer* p, void* stream) {
+  const int rc = validate(p);
+  if (rc != RI_OK) return rc;
+  if (p->n_estimate == 0) return RI_OK;
+  const Layout L = make_layout(*p);
+  uint8_t* sc = static_cast<uint8_t*>(p->d_scratch);
+  const dim3 grid((p->n_estimate + 7) / 8, p->groups);
+  const float scale2 = RI_LOG2E * 0.08838834764831845f;
+  auto* ids = reinterpret_cast<const int32_t*>(sc + L.est_ids);
+  auto* s2 = reinterpret_cast<float*>(sc + L.est_s2);
+  if (p->dtype == RI_BF16)
+    wave_rescore_kernel<RI_BF16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint2*>(p->d_q), static_cast<const uint2*>(p->d_centroids), ids, s2, p->n_centroids, p->group_size,
+        p->n_estimate, L.e_pad, scale2);
+  else
+    wave_rescore_kernel<RI_F16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint2*>(p->d_q), static_cast<const uint2*>(p->d_centroids), ids, s2, p->n_centroids, p->group_size,
+        p->n_estimate, L.e_pad, scale2);
+  RI_LAUNCH_OK("wave_rescore_kernel");
+  return RI_OK;
+}
 
 extern "C" int64_t ri_wave_scratch_bytes(const ri_wave_layer* p) {
   if (validate_geometry_only(p) != RI_OK) return RI_ERR_INVALID;

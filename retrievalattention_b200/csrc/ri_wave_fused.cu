@@ -725,10 +725,12 @@ wave_fused_kernel(FusedArgs f) {
 // After the decode kernel of the same stream: raise this rank's flag on every rank, then wait (bounded) until
 // every rank's flag here holds this step's epoch.  Thread r looks after rank r.
 __global__ void gather_signal_wait_kernel(uint32_t* const* flag_slots, const uint32_t* flags, const uint32_t* epoch,
-                                          int32_t* error, int n_ranks, long long limit_ns) {
+                                          int32_t* error, int n_ranks, long long limit_ns, unsigned long long* stamps) {
   ri_pdl_enter();
   const int r = threadIdx.x;
   if (r >= n_ranks) return;
+  unsigned long long t_in;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_in));
   const uint32_t expected = *epoch;
   // the decode kernel has completed (stream order), so its stores to the other GPUs happen before this fence,
   // and the fence orders them before the flag at system scope
@@ -745,6 +747,12 @@ __global__ void gather_signal_wait_kernel(uint32_t* const* flag_slots, const uin
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
     if ((long long)(now - t0) > limit_ns || ++spins > (1ll << 26)) { *error = 1; break; }   // give up: time or count
     __nanosleep(64);
+  }
+  if (stamps != nullptr) {       // entry | flags raised | last flag seen (the maximum over the threads)
+    unsigned long long t_out;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_out));
+    if (r == 0) { stamps[0] = t_in; stamps[1] = t0; }
+    atomicMax(stamps + 2, t_out);      // the timer only grows, so the latest call's maximum wins
   }
 }
 
@@ -852,7 +860,7 @@ int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const 
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s) {
   const long long limit_ns = (g.wait_limit_us > 0 ? (long long)g.wait_limit_us : 1000000ll) * 1000ll;
   RI_CUDA_OK(ri_launch_pdl_id(6, gather_signal_wait_kernel, dim3(1), dim3(64), 0, s, g.d_flag_slots, g.d_flags, g.d_epoch,
-                              g.d_error, g.n_ranks, limit_ns));
+                              g.d_error, g.n_ranks, limit_ns, g.d_stamps));
   return RI_OK;
 }
 

@@ -154,6 +154,8 @@ class PeerGather:
             raise RuntimeError("PeerGather: the process group does not match the head shards")
         self.epoch = torch.zeros((1,), dtype=torch.int32, device=device)
         self.error = torch.zeros((1,), dtype=torch.int32, device=device)
+        # per layer: the wait kernel's timer readings (entry, flags raised, last flag seen) of its latest call
+        self.stamps = torch.zeros((layers, 3), dtype=torch.int64, device=device)
         esz = self.gathered.element_size()
         out_slots = torch.tensor([[h_out.buffer_ptrs[p] + (l * n + me) * slice_elems * esz for p in range(n)]
                                   for l in range(layers)], dtype=torch.int64)
@@ -171,6 +173,7 @@ class PeerGather:
             g.d_flags = self.flags[l].data_ptr()
             g.d_epoch = self.epoch.data_ptr()
             g.d_error = self.error.data_ptr()
+            g.d_stamps = self.stamps[l].data_ptr()
             self.params.append(g)
         self._C, self._lib = C, _lib
         torch.cuda.synchronize(device)
@@ -187,6 +190,16 @@ class PeerGather:
     def view(self, layer: int) -> torch.Tensor:
         n, b, one, hl, d = self.gathered.shape[1:]
         return self.gathered[layer].permute(1, 2, 0, 3, 4).reshape(b, one, n * hl, d)
+
+    def wait_times_us(self) -> dict:
+        """From the latest wait of every layer: microseconds spent raising the flags (fence + remote stores) and
+        waiting for the last rank's flag, as mean and minimum over the layers.  The minimum of the wait is what the
+        protocol itself costs (the peer was ready), the rest is waiting for a rank that finished its layer later."""
+        st = self.stamps.cpu().double()
+        signal = (st[:, 1] - st[:, 0]) / 1e3
+        wait = (st[:, 2] - st[:, 1]) / 1e3
+        return {"signal_mean": round(float(signal.mean()), 2), "wait_mean": round(float(wait.mean()), 2),
+                "wait_min": round(float(wait.min()), 2), "wait_max": round(float(wait.max()), 2)}
 
     def timed_out(self) -> bool:
         """True when some wait gave up (reads one word from the device)."""

@@ -113,3 +113,50 @@ def test_decode_step_can_be_captured_in_a_graph():
     assert int(cache._per_device["cuda:0"]["static_len"].item()) == 68 + 4
     assert all(torch.isfinite(o.float()).all() for o in outs)
     assert any(not torch.equal(a, b) for a, b in zip(eager2, outs))
+
+
+def test_use_cluster_estimation_attends_clusters_searched_one_layer_ahead():
+    """``use_cluster_estimation``: layer l + 1 attends, with its real query, the clusters that the call for layer l
+    searched with ``queries_next`` (model_hub/LLM.py:102-107, cache_hub/retroinfer_cache.py:582-595).  Against the
+    oracle with the search query and the attending query kept apart; with a perfect estimate the result is the
+    ordinary path's."""
+    from retrievalattention_b200.cache_hub import retroinfer_cache
+
+    batch, layers, kv_heads, q_heads, seq_len, max_new = 2, 3, 2, 8, 2048 + 68, 6
+    cfg = generate_config(seq_len, 0.05, 0.2, n_segments=2)
+    mapping = {str(l): "cuda:0" for l in range(layers)}
+    mk = lambda est: retroinfer_cache([0, 0], layers, batch, seq_len + max_new, kv_heads, q_heads, 128, torch.bfloat16,  # noqa: E731
+                                      mapping, max_new, num_gpus=1, model_size=8, use_cluster_estimation=est,
+                                      **cfg.as_kwargs())
+    ahead, plain = mk(True), mk(False)
+    for cache in (ahead, plain):
+        for b in range(batch):
+            for l in range(layers):
+                k, v = make_kv(kv_heads, seq_len, 128, seed=100 * l + b, device="cuda")
+                cache.prefill_update_kv_cache(None, k, v, l, b)
+        cache.prepare_cache()
+    g = batch * kv_heads
+    for step in range(2):
+        qs = [make_queries(batch, q_heads, 128, seed=500 + 10 * step + l, device="cuda") for l in range(layers)]
+        # layer 1 is searched ahead with a noisy estimate of its query, layer 2 with the exact one
+        guess = [None, (qs[1].float() + 0.3 * torch.randn_like(qs[1].float())).to(torch.bfloat16), qs[2]]
+        for l in range(layers):
+            k_new = make_queries(batch, kv_heads, 128, seed=600 + 10 * step + l, device="cuda")
+            for cache in (ahead, plain):
+                cache.decode_update_kv_cache(k_new, k_new, l)
+            q_next = guess[l + 1] if l + 1 < layers else None
+            out = ahead.compute(qs[l], l, q_next)
+            base = plain.compute(qs[l], l)
+            static_len = 68 + step + 1
+            ref = oat.compute(qs[l].cpu(), ahead.centroids[l].cpu(), ahead.value_sum[l].cpu(), ahead.cluster_size[l].cpu(),
+                              ahead.centroids_mask[l].cpu(), ahead.cluster_count[l].cpu(), ahead.cluster_offset[l].cpu(),
+                              ahead.list_keys[l].cpu().view(g, -1, 128), ahead.list_values[l].cpu().view(g, -1, 128),
+                              ahead.steady_zone_keys[l].cpu().view(g, -1, 128),
+                              ahead.steady_zone_values[l].cpu().view(g, -1, 128), static_len, cfg.nprobe,
+                              cfg.max_compute_cluster_num, cfg.cache_unit_size, ahead.buffer_size,
+                              select_q=None if guess[l] is None else guess[l].cpu())
+            err = (out.cpu().float() - ref.float()).abs()
+            assert err.max() <= 2e-2 and err.mean() <= 2e-3, (step, l, float(err.max()), float(err.mean()))
+            if l != 1:          # no estimate, or a perfect one: the same clusters as the ordinary path
+                assert (out.float() - base.float()).abs().max() <= 1e-2
+    assert not any(ahead._ahead)
