@@ -209,6 +209,19 @@ int ri_rope_split(const void* d_qkv, const float* d_cos_sin, const int64_t* d_po
 int ri_silu_and_mul(const void* d_in, void* d_out, int32_t rows, int32_t inter, int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Dense prefill attention over the prompt, head_dim 128.  Replaces attn_hub/retroinfer_attn.py:4-13
+ * (`retroinfer_prefill_attn`: flash_attn_with_kvcache(q, k_cache, v_cache, causal)) and attn_hub/flash_attn.py:4-13.
+ * d_q, d_out: [batch, seq_len, q_heads, 128]; d_k, d_v: [batch, seq_len, kv_heads, 128] (token-major, contiguous);
+ * query head h attends kv head h / (q_heads / kv_heads); causal != 0: token i sees tokens 0..i.
+ * d_scratch: ri_prefill_attn_scratch_bytes() bytes (the transposed copy of V), contents irrelevant;
+ * d_error: [1], must be zero on entry; set non-zero if a bounded device-side wait ran out.
+ * ------------------------------------------------------------------------------------------ */
+int64_t ri_prefill_attn_scratch_bytes(int32_t batch, int32_t seq_len, int32_t kv_heads);
+int ri_prefill_attn(const void* d_q, const void* d_k, const void* d_v, void* d_out, void* d_scratch, int32_t* d_error,
+                    int32_t batch, int32_t seq_len, int32_t q_heads, int32_t kv_heads, int32_t causal, int32_t dtype,
+                    void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Prefill clustering.  Replaces cache_hub/kmeans.py:224-259 (`segment_k_means`: Triton assign,
  * update, index-add and reverse-index kernels) and, with `center` = 1, also its caller's
  * wrapping in cache_hub/retroinfer_cache.py:416-432 (mean-centring, centroid + mean, sizes in

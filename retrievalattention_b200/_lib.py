@@ -124,6 +124,10 @@ def _load() -> C.CDLL:
     lib.ri_rope_split.argtypes = [C.c_void_p] * 6 + [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_void_p]
     lib.ri_silu_and_mul.restype = C.c_int
     lib.ri_silu_and_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    lib.ri_prefill_attn_scratch_bytes.restype = C.c_int64
+    lib.ri_prefill_attn_scratch_bytes.argtypes = [C.c_int32] * 3
+    lib.ri_prefill_attn.restype = C.c_int
+    lib.ri_prefill_attn.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 6 + [C.c_void_p]
     lib.ri_steady_append.restype = C.c_int
     lib.ri_steady_append.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_int32, C.c_void_p]
     return lib
