@@ -625,6 +625,10 @@ def run_decode(geo, args, rank, world, local_rank, log):
                                      f"per layer; same work here (scan + select stage kernels): {ours * 1e3:.1f} us; whole layer "
                                      f"here (single kernel, attention included): {stage_ms['decode'] * 1e3:.1f} us")
     if world == 1 and not args.no_kmeans and args.config == "cfg1":
+        pf = prefill_summary(geo, log)
+        result["prefill_attn"] = pf
+        cfgd["prefill_attn"] = (f"S=16384 causal: {pf['ms']} ms, {pf['tflops']} TFLOP/s = {pf['frac']} of bf16 peak; flash-attn "
+                                f"library on the same tensors: {pf.get('flash_attn_library_tflops', 'n/a')} TFLOP/s")
         km = kmeans_summary(GEOMETRIES["cfg2"], args, log)
         result["kmeans"] = km
         cfgd["kmeans"] = (f"cfg2 build {km['ms']} ms, {km['tflops']} TFLOP/s = {km['frac']} of sustained bf16 peak "
@@ -751,6 +755,49 @@ def kmeans_summary(geo, args, log):
                         f"{cfg.n_segment} segments, {it} iterations, incl. centring, value sums and layout",
             "ms": round(ms, 3), "tflops": round(tf, 1), "bound": "tensor", "peak": sustained, "peak_kind": "of " + kind,
             "frac": round(tf / sustained, 4), "frac_of_burst_peak": round(tf / burst, 4)}
+
+
+def prefill_summary(geo, log, seq=16384):
+    """Dense causal prefill attention of one request at the model's head geometry: this library's tcgen05 kernel
+    (through ``retroinfer_prefill_attn``) and, beside it, the flash-attn library call the reference makes
+    (attn_hub/retroinfer_attn.py:4-13), on the same tensors.  TFLOP/s over 4*S^2*d*Hq/2 flops."""
+    from retrievalattention_b200.attn_hub import retroinfer_attn as ra
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(7)
+    mk = lambda h: torch.randn((1, seq, h, 128), generator=g, device=dev).to(torch.bfloat16)   # noqa: E731
+    q, k, v = mk(geo.q_heads), mk(geo.kv_heads), mk(geo.kv_heads)
+    flop = 4.0 * seq * seq * 128 * geo.q_heads / 2
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            out = fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps, out
+
+    ms, out = timed(lambda: ra.retroinfer_prefill_attn(q, k, v, True))
+    ra.check_prefill_errors()
+    _, burst, kind = measured_peaks()
+    res = {"workload": f"causal attention over one prompt of {seq} tokens, {geo.q_heads}q/{geo.kv_heads}kv heads, d128, bf16 "
+                       "(V transposed inside the call)",
+           "ms": round(ms, 3), "tflops": round(flop / ms / 1e9, 1), "bound": "tensor", "peak": burst,
+           "peak_kind": "of " + kind, "frac": round(flop / ms / 1e9 / burst, 4)}
+    try:
+        from flash_attn import flash_attn_with_kvcache
+        ms_lib, out_lib = timed(lambda: flash_attn_with_kvcache(q=q, k_cache=k, v_cache=v, causal=True))
+        res["flash_attn_library_ms"] = round(ms_lib, 3)
+        res["flash_attn_library_tflops"] = round(flop / ms_lib / 1e9, 1)
+        res["max_abs_diff_to_library"] = round(float((out.float() - out_lib.float()).abs().max()), 5)
+    except Exception as exc:      # noqa: BLE001 — the comparison is optional
+        res["flash_attn_library"] = "unavailable: " + repr(exc)[:120]
+    log(f"prefill attention: {res}")
+    return res
 
 
 def run_kmeans(geo, args, log):

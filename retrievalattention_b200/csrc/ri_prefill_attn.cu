@@ -5,17 +5,20 @@
 // One CTA per (128 query rows, query head, request); it walks the key/value tiles of 128 tokens the rows may see.
 //   S = Q.K^T      tcgen05.mma, M 128 x N 128 x K 128 (8 x K16), Q and K tiles staged by TMA with the 128-byte
 //                  swizzle straight from the token-major tensors, fp32 accumulator in TMEM (two buffers);
-//   softmax        128 threads, one per query row (= TMEM lane): a row of S comes down with tcgen05.ld, online
-//                  softmax in the log2 domain with a LAZY reference maximum (the running maximum is only adopted
-//                  when it has grown by more than 2^8, so the accumulator is rescaled rarely), P is stored as the
-//                  16-bit A operand of the second product in shared memory, swizzled by the thread itself;
-//   O += P.V       tcgen05.mma again, M 128 x N 128 (channels) x K 128 (keys); its B operand must have the keys
+//   softmax        TWO groups of 128 threads, one thread per query row (= TMEM lane); group g takes the tiles
+//                  j = g, g + 2, ... and keeps its own running (maximum, sum) and its own accumulator, so the
+//                  exponentials of two tiles are computed side by side while the tensor pipe multiplies.  A row of
+//                  S comes down with tcgen05.ld; online softmax in the log2 domain with a LAZY reference maximum
+//                  (the running maximum is only adopted when it has grown by more than 2^8, so an accumulator is
+//                  rescaled rarely); P is stored as the 16-bit A operand of the second product in shared memory,
+//                  swizzled by the thread itself;
+//   O_g += P.V     tcgen05.mma again, M 128 x N 128 (channels) x K 128 (keys); its B operand must have the keys
 //                  contiguous, so V is transposed once beforehand into [request, kv head, channel, token]
 //                  (a pass over V only: S*128*2 bytes per head against S^2*128*2 flops) and its tiles come in by
-//                  TMA like everything else; O stays in TMEM for the whole walk and is rescaled in place
-//                  (tcgen05.ld / tcgen05.st) in the rare case the reference maximum moves.
-// Six warps: TMA producer, MMA issuer, four softmax/epilogue warps.  QK^T of tile j+1 is issued before P.V of tile j,
-// so the tensor pipe works on the next scores while the softmax warps are busy with the current ones.
+//                  TMA like everything else; O_0 and O_1 stay in TMEM for the whole walk (S_0 | S_1 | O_0 | O_1 =
+//                  all 512 columns), are rescaled in place (tcgen05.ld / tcgen05.st) in the rare case a reference
+//                  maximum moves, and are merged by log-sum-exp at the end.
+// Ten warps: TMA producer, MMA issuer, eight softmax/epilogue warps.  QK^T of tile j+1 is issued before P.V of tile j.
 // Every mbarrier wait is bounded; on expiry the kernel records where, releases its TMEM and returns.
 #include <cuda.h>
 
@@ -29,10 +32,10 @@ using namespace ri_tc;
 constexpr int kTile = 128;                 // query rows per CTA, keys per step
 constexpr int kHalf = kTile * 128;         // bytes of a 128-row x 64-element operand half-tile
 constexpr int kKvStages = 2;
-constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 512;        // S buffer 0 | S buffer 1 | O | (unused)
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;        // S_0 | S_1 | O_0 | O_1, 128 columns each
 constexpr int kSmem = 1024 /*align*/ + 2 * kHalf /*Q*/ + kKvStages * 2 * kHalf /*K*/ + kKvStages * 2 * kHalf /*V^T*/ +
-                      2 * kHalf /*P*/ + 256 /*barriers*/;
+                      2 * 2 * kHalf /*P_0, P_1*/ + 256 /*barriers*/;
 constexpr float kLazy = 8.0f;              // the reference maximum follows the running one in steps of more than 2^8
 
 struct AttnArgs {
@@ -68,7 +71,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base, sK = sQ + 2 * kHalf, sV = sK + kKvStages * 2 * kHalf, sP = sV + kKvStages * 2 * kHalf;
-  const uint32_t bars = sP + 2 * kHalf;
+  const uint32_t bars = sP + 2 * 2 * kHalf;
   uint8_t* sP_ptr = smem_raw + (sP - smem_u32(smem_raw));
   const uint32_t bar_q = bars;
   auto bar_k_full = [&](int s) { return bars + 8u * (1 + s); };
@@ -77,9 +80,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   auto bar_v_empty = [&](int s) { return bars + 8u * (7 + s); };
   auto bar_s_full = [&](int b) { return bars + 8u * (9 + b); };
   auto bar_s_empty = [&](int b) { return bars + 8u * (11 + b); };
-  const uint32_t bar_p_full = bars + 8u * 13, bar_pv_done = bars + 8u * 14;
+  auto bar_p_full = [&](int g) { return bars + 8u * (13 + g); };
+  auto bar_pv_done = [&](int g) { return bars + 8u * (15 + g); };
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_skip;
+  __shared__ float s_m1[kTile], s_l1[kTile];      // group 1's running (maximum, sum) per row, for the final merge
 
   if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(a.error_flag);
   __syncthreads();
@@ -99,8 +104,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(bar_v_full(s), 1); mbar_init(bar_v_empty(s), 1);
     }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_s_full(i), 1); mbar_init(bar_s_empty(i), 4); }
-    mbar_init(bar_p_full, 4);
-    mbar_init(bar_pv_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_p_full(i), 4); mbar_init(bar_pv_done(i), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -111,7 +115,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tmem_o = tmem + 2 * kTile;
   volatile int* abort_flag = &s_abort;
 
   if (warp == 0) {
@@ -149,19 +152,19 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       bool ok = mbar_wait(bar_q, 0, abort_flag, 23);
-      auto issue_pv = [&](int t) {
-        const int s = t % kKvStages;
-        if (!mbar_wait(bar_p_full, t & 1, abort_flag, 24)) return false;
+      auto issue_pv = [&](int t) {          // tile t belongs to softmax group t & 1: its P buffer, its accumulator
+        const int s = t % kKvStages, g = t & 1;
+        if (!mbar_wait(bar_p_full(g), (t >> 1) & 1, abort_flag, 24)) return false;
         if (!mbar_wait(bar_v_full(s), (t / kKvStages) & 1, abort_flag, 25)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t da = umma_desc_sw128(sP + kb * kHalf), db = umma_desc_sw128(sV + s * 2 * kHalf + kb * kHalf);
+          const uint64_t da = umma_desc_sw128(sP + (g * 2 + kb) * kHalf), db = umma_desc_sw128(sV + s * 2 * kHalf + kb * kHalf);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma_f16(tmem_o, da + 2 * k, db + 2 * k, a.idesc, (t | kb | k) != 0);
+          for (int k = 0; k < 4; ++k) tc_mma_f16(tmem + (2 + g) * kTile, da + 2 * k, db + 2 * k, a.idesc, ((t >> 1) | kb | k) != 0);
         }
         tc_commit(bar_v_empty(s));
-        tc_commit(bar_pv_done);
+        tc_commit(bar_pv_done(g));
         return true;
       };
       for (int j = 0; ok && j < n_kv; ++j) {
@@ -183,65 +186,72 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (ok) issue_pv(n_kv - 1);
     }
   } else {
-    // ---------------- softmax and epilogue: thread = query row = TMEM lane ----------------
+    // ---------------- softmax and epilogue: thread = query row = TMEM lane; group g owns tiles g, g+2, ... ----------------
+    const int grp = (warp - 2) >> 2;                       // 0 or 1
     const int lane_group = warp & 3;                       // a warp may touch only its quarter of the TMEM lanes
     const int row = lane_group * 32 + lane;                // row of the tile
     const int q_row = q_row0 + row;                        // position of the query in its request
     const uint32_t t_lane = (uint32_t)(lane_group * 32) << 16;
+    const uint32_t tmem_s = tmem + grp * kTile, tmem_o = tmem + (2 + grp) * kTile;
+    uint8_t* my_p = sP_ptr + grp * 2 * kHalf;
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; ok && j < n_kv; ++j) {
-      const int buf = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(buf), (j >> 1) & 1, abort_flag, 31));
+    int k = 0;                                             // this group's tiles done
+    for (int j = grp; ok && j < n_kv; j += 2, ++k) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(grp), k & 1, abort_flag, 31));
       if (!ok) break;
       tc_fence_after();
       uint32_t sr[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tc_ld32(tmem + t_lane + buf * kTile + c * 32, sr[c]);
+      for (int c = 0; c < 4; ++c) tc_ld32(tmem_s + t_lane + c * 32, sr[c]);
       tc_wait_ld();
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_landed(sr[c]);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_empty(buf));        // this warp's quarter of the scores is in registers
+      if (lane == 0) mbar_arrive(bar_s_empty(grp));        // this warp's quarter of the scores is in registers
 
-      // scaled, masked scores and their maximum
+      // masked scores (edge tiles only) and the row maximum, on the raw products (the scale is positive)
       const int col0 = j * kTile;
       const bool edge = col0 + kTile > a.S || (a.causal && col0 + kTile - 1 > q_row);
-      float m_tile = -INFINITY;
+      float m_raw = -INFINITY;
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + c * 32 + i;
+            if (col >= a.S || (a.causal && col > q_row)) sr[c][i] = 0xff800000u;     // -inf
+          }
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sr[c][i]) * a.scale2;
-          if (edge) {
-            const int col = col0 + c * 32 + i;
-            if (col >= a.S || (a.causal && col > q_row)) x = -INFINITY;
-          }
-          sr[c][i] = __float_as_uint(x);
-          m_tile = fmaxf(m_tile, x);
-        }
+        for (int i = 0; i < 32; ++i) m_raw = fmaxf(m_raw, __uint_as_float(sr[c][i]));
+      const float m_tile = m_raw * a.scale2;
       // lazy reference maximum: adopt the running maximum only when it has grown by more than kLazy
-      const bool move = m_tile > m_ref + kLazy;            // also true for the first tile (m_ref = -inf)
+      const bool move = m_tile > m_ref + kLazy;            // also true for the group's first tile (m_ref = -inf)
       const float m_new = move ? m_tile : m_ref;
       const float factor = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);      // 1 when the maximum stays
-      // probabilities, packed as the 16-bit operand of the second product
-      uint32_t pk[64];
+      // probabilities p = 2^(s * scale - m), packed in place as the 16-bit operand of the second product:
+      // word w of the row = columns 2w, 2w+1 (it overwrites the scores already consumed)
       float lsum = 0.f;
+      const float neg_m = -m_new;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(__uint_as_float(sr[c][i]) - m_new), p1 = exp2f(__uint_as_float(sr[c][i + 1]) - m_new);
+          const float p0 = exp2f(fmaf(__uint_as_float(sr[c][i]), a.scale2, neg_m));
+          const float p1 = exp2f(fmaf(__uint_as_float(sr[c][i + 1]), a.scale2, neg_m));
           lsum += p0 + p1;
-          pk[c * 16 + i / 2] = Elem<DT>::pack2(p0, p1);
+          sr[c][i / 2] = Elem<DT>::pack2(p0, p1);
         }
       l_run = l_run * factor + lsum;
       m_ref = m_new;
 
-      // P's buffer and the accumulator are free once the previous tile's second product has completed
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag, 32));
+      // this group's P buffer and accumulator are free once its previous tile's second product has completed
+      if (k > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(grp), (k - 1) & 1, abort_flag, 32));
         if (!ok) break;
         tc_fence_after();
         if (__any_sync(0xffffffffu, move)) {               // rare: bring this warp's rows of O to the new reference
@@ -264,36 +274,46 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           const uint32_t off = hf * kHalf + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(sP_ptr + off) =
-              make_uint4(pk[hf * 32 + ch * 4], pk[hf * 32 + ch * 4 + 1], pk[hf * 32 + ch * 4 + 2], pk[hf * 32 + ch * 4 + 3]);
+          const int c = hf * 2 + (ch >> 2), w = (ch & 3) * 4;     // columns hf*64 + ch*8 .. +7 = words w..w+3 of chunk c
+          *reinterpret_cast<uint4*>(my_p + off) = make_uint4(sr[c][w], sr[c][w + 1], sr[c][w + 2], sr[c][w + 3]);
         }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> the MMA's async reads
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full);
+      if (lane == 0) mbar_arrive(bar_p_full(grp));
     }
-    // ---- epilogue: O / l, one row per thread ----
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv_done, (n_kv - 1) & 1, abort_flag, 33));
-    if (ok) {
-      tc_fence_after();
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    // ---- epilogue: wait for the group's last product; group 1 hands its (maximum, sum) over; group 0 merges the two
+    //      accumulators by log-sum-exp, divides and stores, one row per thread ----
+    if (ok && k > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(grp), (k - 1) & 1, abort_flag, 33));
+    if (grp == 1) { s_m1[row] = m_ref; s_l1[row] = l_run; }
+    tc_fence_before();
+    asm volatile("bar.sync 1, 256;" ::: "memory");         // the eight softmax warps, always reached (also after a give-up)
+    tc_fence_after();
+    if (grp == 0 && ok && !*abort_flag) {
+      const float m1 = s_m1[row], l1 = s_l1[row];
+      const float M = fmaxf(m_ref, m1);                    // group 0 always has a tile: finite
+      const float f0 = exp2f(m_ref - M), f1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+      const float l = l_run * f0 + l1 * f1;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const float w0 = f0 * inv, w1 = f1 * inv;
+      const bool two = n_kv > 1;                           // O_1 holds nothing when group 1 had no tile
       uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + (((int64_t)b * a.S + q_row) * a.Hq + h) * 128);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        uint32_t orow[32];
-        tc_ld32(tmem_o + t_lane + c * 32, orow);
+        uint32_t o0[32], o1[32];
+        tc_ld32(tmem + 2 * kTile + t_lane + c * 32, o0);
+        if (two) tc_ld32(tmem + 3 * kTile + t_lane + c * 32, o1);
         tc_wait_ld();
-        tc_ld_landed(orow);
+        tc_ld_landed(o0);
+        if (two) tc_ld_landed(o1);
         if (q_row < a.S) {
+          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = Elem<DT>::pack2(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
-            w.y = Elem<DT>::pack2(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-            w.z = Elem<DT>::pack2(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
-            w.w = Elem<DT>::pack2(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
-            dst[c * 4 + i / 8] = w;
-          }
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o0[i]) * w0 + (two ? __uint_as_float(o1[i]) * w1 : 0.f);
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            dst[c * 4 + i / 8] = make_uint4(Elem<DT>::pack2(v[i], v[i + 1]), Elem<DT>::pack2(v[i + 2], v[i + 3]),
+                                            Elem<DT>::pack2(v[i + 4], v[i + 5]), Elem<DT>::pack2(v[i + 6], v[i + 7]));
         }
       }
     }
