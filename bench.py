@@ -683,6 +683,71 @@ def run_cfg4(args, rank, world, local_rank, device, dist, cpu_group, log):
     return out
 
 
+def run_host_tier(geo, args, log):
+    """``--kv-on-host``: the configuration's geometry with the cluster store in pinned host memory and an LRU page cache
+    on the GPU (the reference's tiers), ``--layers`` of its layers (pinned memory is the limit), eager stepping (the host
+    takes part in every layer).  Two query streams: fresh Gaussian queries every step (no temporal locality: the worst
+    case for the page cache) and slowly drifting ones (q_t = 0.95 q_{t-1} + 0.31 noise).  Reports tokens/s, the page
+    cache's hit rate and the host-to-device bytes of the missed pages per second."""
+    from retrievalattention_b200.cache_hub import retroinfer_cache
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    cfg = geo.index()
+    steps, warm = args.steps, max(args.warmup, 3)
+    max_new = 2 * (steps + warm) + 4
+    mapping = {str(l): str(device) for l in range(geo.layers)}
+    cache = retroinfer_cache([0] * geo.batch, geo.layers, geo.batch, geo.context + max_new, geo.kv_heads, geo.q_heads, 128,
+                             torch.bfloat16, mapping, max_new, num_gpus=1, model_size=8, kv_on_host=True,
+                             stage_misses=not args.uva_misses, **cfg.as_kwargs())
+    for l in range(geo.layers):
+        for b in range(geo.batch):
+            k, v = make_kv(geo.kv_heads, geo.context, 128, seed=l * 1000 + b, theta=geo.rope_theta, device=device)
+            cache.prefill_update_kv_cache(None, k, v, l, b)
+        log(f"set-up: layer {l + 1}/{geo.layers} indexed")
+    cache.prepare_cache()
+    g = torch.Generator(device=device).manual_seed(5)
+    rnd = lambda h: torch.randn((geo.batch, 1, h, 128), generator=g, device=device).to(torch.bfloat16)   # noqa: E731
+    results = {}
+    for name, keep in (("fresh queries", 0.0), ("drifting queries", 0.95)):
+        q = [rnd(geo.q_heads).float() for _ in range(geo.layers)]
+        pages = [0, 0]
+
+        def step(count):
+            for l in range(geo.layers):
+                q[l] = keep * q[l] + (1 - keep * keep) ** 0.5 * rnd(geo.q_heads).float()
+                cache.decode_update_kv_cache(rnd(geo.kv_heads), rnd(geo.kv_heads), l)
+                cache.compute(q[l].to(torch.bfloat16), l)
+                if count:
+                    pages[0] += int(cache.page_lists[l][3].sum())
+                    pages[1] += int(cache.page_lists[l][7].sum())
+        for _ in range(warm):
+            step(False)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step(True)
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        hit, miss = pages
+        results[name] = {"tok_s": round(geo.batch * steps / sec, 1), "ms_per_step": round(sec / steps * 1e3, 3),
+                         "page_hit_rate": round(hit / max(hit + miss, 1), 4),
+                         "missed_page_gbs": round(miss * 8 * 128 * 2 * 2 / sec / 1e9, 2)}
+        log(f"{name}: {results[name]}")
+    main = results["drifting queries"]
+    print(json.dumps({
+        "metric": METRIC, "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"{geo.name}: host tier (cluster store in pinned host memory, GPU page cache of "
+                               f"{cfg.cache_cluster_num} clusters per group), {geo.layers} layers, batch {geo.batch}, ctx {geo.context}, "
+                               f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; missed pages "
+                               + ("read through UVA by the copy kernel" if args.uva_misses else
+                                  "staged by host threads, one strided copy per tensor and layer on a side stream"),
+                   "timing": "wall clock around eager steps (the host takes part in every layer)"},
+        "host_tier": results}), flush=True)
+
+
 def reference_arm(geo, args, log):
     """The reference's own arithmetic for this path on the host cores (oracle port): each step is one
     layer of the workload (all groups), scaled to a full decode step."""
@@ -862,6 +927,10 @@ def main():
                     help="skip the whole-model decode step (projections, MLP, vocabulary head with random weights around "
                          "the same caches; key decode_model, single GPU)")
     ap.add_argument("--no-kmeans", action="store_true", help="skip the short clustering run (key kmeans, single GPU)")
+    ap.add_argument("--kv-on-host", action="store_true",
+                    help="time the host tier of --config (cluster store in pinned host memory, GPU page cache), --layers layers")
+    ap.add_argument("--uva-misses", action="store_true",
+                    help="with --kv-on-host: the reference's pattern (the copy kernel reads missed pages through UVA)")
     ap.add_argument("--no-cfg4", action="store_true",
                     help="several GPUs: skip the run of configuration 4 (72B geometry, heads sharded) after the main one")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
@@ -882,6 +951,10 @@ def main():
     if args.config == "cfg2":
         if rank == 0:
             run_kmeans(geo, args, log)
+        return
+    if args.kv_on_host:
+        if rank == 0:
+            run_host_tier(geo, args, log)
         return
     run_decode(geo, args, rank, world, local_rank, log)
     if world > 1:

@@ -128,6 +128,12 @@ int ri_wave_rescore(const ri_wave_layer* p, void* stream);
 int ri_wave_attend_buffer(const ri_wave_layer* p, const void* d_exec_keys, const void* d_exec_values,
                           int32_t exec_stride, const int32_t* d_valid_lengths, void* stream);
 
+/* The same, also returning the log-sum-exp (natural log) of every (group, head) in d_lse_out [G, gs], so that the result can
+ * be merged with attention over further rows (ri_weighted_flash_decoding with d_previous_out/d_previous_lse): the host tier
+ * attends the estimation zone and the steady zone while the missed pages are still on their way from the host. */
+int ri_wave_attend_buffer_lse(const ri_wave_layer* p, const void* d_exec_keys, const void* d_exec_values,
+                              int32_t exec_stride, const int32_t* d_valid_lengths, float* d_lse_out, void* stream);
+
 /* ---- several GPUs: the output gather done by the decode kernel itself ------------------------------
  * The path shards by (request, KV head) group with no exchange inside the attention; the one
  * exchange is the gather of the ranks' [G, gs, 128] output slices before the model's output
@@ -349,6 +355,18 @@ int ri_wb_append_clusters(ri_wave_buffer* wb, const int32_t* cluster_sizes, int3
  * Returns the number of groups whose retrieval was cut by the page budget (>= 0) or an error. */
 int ri_wb_batch_access(ri_wave_buffer* wb);
 int ri_wb_sync(ri_wave_buffer* wb);          /* waits for the background update (update lists valid) */
+/* Between ri_wb_batch_access and the execution-buffer assembly: the worker threads copy every missed page from the cluster
+ * store in host memory (h_src_*: [groups, src_rows_per_group] rows of row_bytes) into a pinned staging area
+ * (h_stage_*: [groups, stage_rows_per_group] rows), page j of group g at row miss_cumsum[g][j]; blocks until done and
+ * returns the largest number of staged rows of any group in *max_rows_out.  ri_stage_upload then sends the first `rows` rows
+ * of every group's slot to the device-side staging buffers with ONE strided copy per tensor on `stream`, and
+ * ri_gather_copy_and_concat reads the pages from there (data_offsets2 = miss_cumsum).  The reference's kernel reads the
+ * missed pages from pinned memory through UVA instead (library/.../gather_copy.cu:100-212, cache_hub/retroinfer_cache.py:642-648). */
+int ri_wb_stage_misses(ri_wave_buffer* wb, const void* h_src_keys, const void* h_src_values, int64_t src_rows_per_group,
+                       void* h_stage_keys, void* h_stage_values, int64_t stage_rows_per_group, int32_t row_bytes,
+                       int32_t* max_rows_out);
+int ri_stage_upload(void* d_stage_keys, void* d_stage_values, const void* h_stage_keys, const void* h_stage_values,
+                    int32_t groups, int64_t stage_rows_per_group, int32_t rows, int32_t row_bytes, void* stream);
 int64_t ri_wb_rows_used(const ri_wave_buffer* wb, int32_t group);
 
 #ifdef __cplusplus

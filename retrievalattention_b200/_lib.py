@@ -105,6 +105,14 @@ def _load() -> C.CDLL:
     lib.ri_wb_batch_access.argtypes = [C.c_void_p]
     lib.ri_wb_sync.restype = C.c_int
     lib.ri_wb_sync.argtypes = [C.c_void_p]
+    lib.ri_wb_stage_misses.restype = C.c_int
+    lib.ri_wb_stage_misses.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
+                                       C.c_int32, C.POINTER(C.c_int32)]
+    lib.ri_stage_upload.restype = C.c_int
+    lib.ri_stage_upload.argtypes = [C.c_void_p] * 4 + [C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
+    lib.ri_wave_attend_buffer_lse.restype = C.c_int
+    lib.ri_wave_attend_buffer_lse.argtypes = [C.POINTER(WaveLayer), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+                                              C.c_void_p]
     lib.ri_wb_rows_used.restype = C.c_int64
     lib.ri_wb_rows_used.argtypes = [C.c_void_p, C.c_int32]
     lib.ri_batch_gemm_softmax.restype = C.c_int

@@ -12,13 +12,18 @@ offload, no CPU re-layout).  Two storage tiers:
 * default (``kv_on_host=False``): the whole cluster-contiguous KV stays in HBM and one decode layer is
   one ``ri_wave_decode_layer`` call with no host synchronisation.  ``core`` and ``cache_cluster_num``
   are accepted but unused — nothing lives on the host, so there is no page cache to size.
-* ``kv_on_host=True`` (not a reference argument): the reference's arrangement — cluster-contiguous KV
+* ``kv_on_host=True`` (not a reference argument): the reference's tiers — cluster-contiguous KV
   in pinned host memory (:264-274), an LRU page cache of ``cache_cluster_num`` clusters on the GPU
   (:204-211), a host-side wave buffer per layer (:117-121) and an execution buffer assembled per step
-  (:642-648).  Per layer: scan + select on the GPU, the retrieved ids go to the host (blocking copy,
-  as :575), the wave buffer produces hit/miss page lists, ``gather_copy_and_concat`` reads the missed
-  pages straight from pinned memory, the attend stage runs on the execution buffer, and
+  (:642-648).  Per layer: scan + select on the GPU, the select stage writes the retrieved ids straight into
+  pinned host memory and the host waits on an event (instead of the blocking copy of :575); while the host
+  walks the LRU lists and its worker threads copy the missed pages into a pinned staging area, the GPU already
+  attends the estimation zone and the steady zone; the staged pages go up with one strided copy per tensor
+  on a side stream; behind that copy's event ``gather_copy_and_concat`` appends missed and hit pages to the
+  execution buffer, the second attention pass covers them and merges by log-sum-exp, and
   ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
+  ``stage_misses=False`` keeps the reference's own pattern (the copy kernel reads the missed pages from pinned
+  memory through UVA, one attention pass).
 
 After every 1024 generated tokens ``decode_update_kv_cache`` folds them into the index (``_update_kv_cache``,
 :462-524), provided ``max_new_length`` announced that many at construction.
@@ -51,7 +56,7 @@ class retroinfer_cache(KV_Cache):
                  static_pattern_start: int, static_pattern_end: int, core: int, n_centroids: int, n_segment: int,
                  nprobe: int, max_compute_cluster_num: int, cache_unit_size: int, cache_cluster_num: int,
                  num_gpus: int, model_size: int, use_cluster_estimation: bool = False,
-                 kv_on_host: bool = False, fuse_append: bool = True) -> None:
+                 kv_on_host: bool = False, fuse_append: bool = True, stage_misses: bool = True) -> None:
         super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
                          layer_mapping, num_gpus, model_size)
         if head_dim != 128:
@@ -91,6 +96,7 @@ class retroinfer_cache(KV_Cache):
         self.list_stride = self.input_length - self.static_pattern_total + self.input_length_new
 
         self.kv_on_host = bool(kv_on_host)
+        self.stage_misses = bool(stage_misses) and self.kv_on_host
         g, c, d = self.batch_groups, n_centroids, head_dim
         self.steady_zone_keys, self.steady_zone_values = [], []
         self.centroids, self.value_sum, self.cluster_size = [], [], []
@@ -173,6 +179,23 @@ class retroinfer_cache(KV_Cache):
             per["exec_keys"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
             per["exec_values"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
             per["valid_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+            if self.stage_misses:
+                # two staging areas used alternately (the host refills one while the other's copy may still be running),
+                # on the host (pinned) and on the device; one side stream and one event per area
+                rows = self.buffer_size * self.page_size
+                per["stage_rows"] = rows
+                per["stage_host"] = [tuple(torch.zeros((g, rows, d), dtype=self.dtype, pin_memory=True) for _ in range(2))
+                                     for _ in range(2)]
+                per["stage_dev"] = [tuple(torch.zeros((g, rows, d), dtype=self.dtype, device=dev) for _ in range(2))
+                                    for _ in range(2)]
+                per["copy_stream"] = torch.cuda.Stream(device=dev)
+                per["uploaded"] = [torch.cuda.Event() for _ in range(2)]
+                per["selected"] = torch.cuda.Event()
+                per["lse"] = torch.zeros((g, self.group_size), dtype=torch.float32, device=dev)
+                per["part"] = torch.zeros((g, self.group_size, d), dtype=self.dtype, device=dev)
+                per["steady_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+                per["rest_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+                per["turn"] = 0
         self._keep_alive = []
 
     # ------------------------------------------------------------------ prefill
@@ -247,6 +270,10 @@ class retroinfer_cache(KV_Cache):
                 steady_keys=self.steady_zone_keys[ldx].view(g, self.static_stride, self.head_dim),
                 steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
                 static_len=per["static_len"], scratch=self._scratch_for(ldx, per))
+            if self.stage_misses:
+                # the select stage stores the ranked ids straight into the pinned array the host wave buffer reads
+                self._layers[ldx].retrieved_ids = self.cluster_ids[ldx]
+                self._layers[ldx].params.d_retrieved_ids = self.cluster_ids[ldx].data_ptr()
 
     def _scratch_for(self, ldx, per):
         """One scratch per device; with ``use_cluster_estimation`` one per layer (a search made ahead must survive
@@ -398,6 +425,8 @@ class retroinfer_cache(KV_Cache):
         static_len = self.static_pattern_total if layer_idx == self.layer_num - 1 else self.static_pattern_total + 1
         layer.stage("scan", queries, out)
         layer.stage("select", queries, out)
+        if self.stage_misses:
+            return self._finish_host_tier_staged(queries, layer_idx, out, static_len)
         self.cluster_ids[layer_idx].copy_(layer.retrieved_ids)          # blocking device-to-host copy (:575)
         wb.batch_access()                                                # hit/miss page lists; LRU update in background
         (hit_ids, hit_sizes, hit_cum, hit_n, miss_ids, miss_sizes, miss_cum, miss_n,
@@ -417,3 +446,75 @@ class retroinfer_cache(KV_Cache):
                                 upd_cache, upd_n, g, self.execution_stride, self.cache_size, self.buffer_size,
                                 static_len)
         return out
+
+    def _finish_host_tier_staged(self, queries, layer_idx, out, static_len):
+        """The rest of a host-tier layer with the missed pages staged by the host and sent up on a side stream (what the
+        reference does with UVA reads inside its copy kernel, :642-648), overlapped with the first attention pass."""
+        import ctypes as C
+
+        from .. import _lib
+        from ..kernels import gather_copy_and_concat, gather_copy_and_scatter
+
+        layer, wb = self._layers[layer_idx], self.wave_buffer[layer_idx]
+        dev = self.layer_mapping[str(layer_idx)]
+        per = self._per_device[dev]
+        g, d, gs = self.batch_groups, self.head_dim, self.group_size
+        main = torch.cuda.current_stream(dev)
+        per["selected"].record(main)
+        (hit_ids, hit_sizes, hit_cum, hit_n, miss_ids, miss_sizes, miss_cum, miss_n,
+         upd_buf, upd_sizes, upd_cache, upd_n) = self.page_lists[layer_idx]
+        sk = self.steady_zone_keys[layer_idx].view(g, self.static_stride, d)
+        sv = self.steady_zone_values[layer_idx].view(g, self.static_stride, d)
+        lk = self.list_keys[layer_idx].view(g, self.list_stride, d)
+        lv = self.list_values[layer_idx].view(g, self.list_stride, d)
+        ek, ev, lens = per["exec_keys"], per["exec_values"], per["valid_lengths"]
+        # 1. nothing of this needs the host: the steady rows into the execution buffer (a concat without pages), then the
+        #    estimation zone + steady zone attention, with its log-sum-exp
+        zero = self._zero_counts(dev, g)
+        gather_copy_and_concat(sk, per["stage_dev"][0][0], self.cache_keys[layer_idx], ek, sv, per["stage_dev"][0][1],
+                               self.cache_values[layer_idx], ev, miss_cum, miss_sizes, miss_cum, zero, hit_ids, hit_sizes,
+                               hit_cum, zero, per["steady_lengths"], g, self.static_stride, per["stage_rows"],
+                               self.cache_size, self.execution_stride, self.buffer_size, static_len)
+        layer._bind(queries, per["part"].view_as(queries))
+        _lib.check(_lib.lib.ri_wave_attend_buffer_lse(C.byref(layer.params), ek.data_ptr(), ev.data_ptr(), ek.shape[1],
+                                                      per["steady_lengths"].data_ptr(), per["lse"].data_ptr(),
+                                                      _lib.current_stream()), "ri_wave_attend_buffer_lse")
+        # 2. host: ids are in pinned memory once the select stage is done; LRU walk; worker threads stage the missed pages
+        per["selected"].synchronize()
+        wb.batch_access()
+        turn = per["turn"]
+        per["turn"] = turn ^ 1
+        per["uploaded"][turn].synchronize()          # the area's previous copy (two layers ago) is long done
+        hk, hv = per["stage_host"][turn]
+        dk, dv = per["stage_dev"][turn]
+        rows = C.c_int32(0)
+        _lib.check(_lib.lib.ri_wb_stage_misses(wb._h, lk.data_ptr(), lv.data_ptr(), self.list_stride, hk.data_ptr(),
+                                               hv.data_ptr(), per["stage_rows"], d * 2, C.byref(rows)), "ri_wb_stage_misses")
+        with torch.cuda.stream(per["copy_stream"]):
+            _lib.check(_lib.lib.ri_stage_upload(dk.data_ptr(), dv.data_ptr(), hk.data_ptr(), hv.data_ptr(), g,
+                                                per["stage_rows"], rows.value, d * 2, per["copy_stream"].cuda_stream),
+                       "ri_stage_upload")
+            per["uploaded"][turn].record(per["copy_stream"])
+        # 3. behind the copy: missed pages (from the device staging area) and hit pages behind the steady rows, the second
+        #    attention pass over them, merged with the first by log-sum-exp
+        main.wait_event(per["uploaded"][turn])
+        gather_copy_and_concat(sk, dk, self.cache_keys[layer_idx], ek, sv, dv, self.cache_values[layer_idx], ev,
+                               miss_cum, miss_sizes, miss_cum, miss_n, hit_ids, hit_sizes, hit_cum, hit_n, lens, g,
+                               self.static_stride, per["stage_rows"], self.cache_size, self.execution_stride,
+                               self.buffer_size, static_len)
+        torch.sub(lens, static_len, out=per["rest_lengths"])
+        off = static_len * d * ek.element_size()
+        _lib.check(_lib.lib.ri_weighted_flash_decoding(
+            queries.data_ptr(), ek.data_ptr() + off, ev.data_ptr() + off, None, per["rest_lengths"].data_ptr(),
+            per["part"].data_ptr(), per["lse"].data_ptr(), out.data_ptr(), None, g, gs, self.execution_stride,
+            _lib.dtype_code(self.dtype), _lib.current_stream()), "ri_weighted_flash_decoding")
+        wb.sync()                                     # update lists are final (:682)
+        gather_copy_and_scatter(ek, self.cache_keys[layer_idx], ev, self.cache_values[layer_idx], upd_buf, upd_sizes,
+                                upd_cache, upd_n, g, self.execution_stride, self.cache_size, self.buffer_size, static_len)
+        return out
+
+    def _zero_counts(self, dev, g):
+        per = self._per_device[dev]
+        if "zero_counts" not in per:
+            per["zero_counts"] = torch.zeros((g,), dtype=torch.int32, pin_memory=True)
+        return per["zero_counts"]

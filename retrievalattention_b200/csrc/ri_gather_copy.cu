@@ -164,6 +164,21 @@ extern "C" int ri_gather_copy_and_concat(const void* key_data1, const void* key_
   return RI_OK;
 }
 
+// One strided host-to-device copy per tensor: the first `rows` rows of every group's slot of the staging area
+// (what ri_wb_stage_misses filled) go to the same place of the device-side staging buffers.
+extern "C" int ri_stage_upload(void* d_stage_keys, void* d_stage_values, const void* h_stage_keys, const void* h_stage_values,
+                               int32_t groups, int64_t stage_rows_per_group, int32_t rows, int32_t row_bytes, void* stream) {
+  RI_REQUIRE(d_stage_keys && d_stage_values && h_stage_keys && h_stage_values, "ri_stage_upload: null pointer");
+  RI_REQUIRE(groups > 0 && stage_rows_per_group > 0 && row_bytes > 0 && rows >= 0 && rows <= stage_rows_per_group,
+             "ri_stage_upload: bad sizes");
+  if (rows == 0) return RI_OK;
+  const size_t pitch = (size_t)stage_rows_per_group * row_bytes, width = (size_t)rows * row_bytes;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RI_CUDA_OK(cudaMemcpy2DAsync(d_stage_keys, pitch, h_stage_keys, pitch, width, groups, cudaMemcpyHostToDevice, s));
+  RI_CUDA_OK(cudaMemcpy2DAsync(d_stage_values, pitch, h_stage_values, pitch, width, groups, cudaMemcpyHostToDevice, s));
+  return RI_OK;
+}
+
 extern "C" int ri_gather_copy_and_scatter(const void* key_data, void* key_buffer, const void* value_data,
                                           void* value_buffer, const int32_t* s_offsets, const int32_t* copy_sizes,
                                           const int32_t* d_offsets, const int32_t* copy_chunks, int32_t groups,

@@ -6,10 +6,8 @@
 //            N = 128 centroids, K = 128 channels as 8 x K16) with operands staged by TMA
 //            (128-byte swizzle) and fp32 accumulators in TMEM; a warp-specialised CTA
 //            (TMA producer / MMA issuer / epilogue warps) overlaps the running arg-max of one
-//            accumulator buffer with the MMAs into the other.  Two forms: the wide one (256
-//            tokens per block, persistent over blocks, eight epilogue warps) is what the build
-//            launches; the narrow one (128 tokens per CTA, four epilogue warps) stays for
-//            comparison (RI_KMEANS_NARROW=1).
+//            accumulator buffer with the MMAs into the other: 256 tokens per block, persistent
+//            over blocks, eight epilogue warps.
 //   bucket   stable counting sort of the tokens of a problem by cluster: counts, offsets and
 //            the member list in ascending token order (deterministic, no global atomics).
 //   update   one warp per cluster sums its member rows in list order (fp32), forms the mean,
@@ -32,11 +30,7 @@ using namespace ri_tc;
 
 constexpr int kTileM = 128;       // tokens per CTA tile
 constexpr int kTileN = 128;       // centroids per MMA tile
-constexpr int kStages = 4;        // centroid-tile pipeline depth
-constexpr int kAssignThreads = 192;
-constexpr uint32_t kTmemCols = 256;   // two 128-column accumulator buffers
 constexpr int kHalfBytes = kTileM * 128;   // one K-block (64 channels) of a 128-row tile: 16 KB
-constexpr int kAssignSmem = 1024 /*align*/ + 2 * kHalfBytes /*A*/ + kStages * 2 * kHalfBytes /*B*/ + 256 /*barriers*/;
 
 // ---- assign ---------------------------------------------------------------------------------
 struct AssignArgs {
@@ -49,151 +43,8 @@ struct AssignArgs {
   uint32_t idesc;
 };
 
-__global__ void __launch_bounds__(kAssignThreads, 1)
-kmeans_assign_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_constant__ CUtensorMap map_cent,
-                     AssignArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // SW128 tiles need 1024-byte alignment
-  const uint32_t sA = base;
-  const uint32_t sB = base + 2 * kHalfBytes;
-  const uint32_t bars = sB + kStages * 2 * kHalfBytes;
-  const uint32_t bar_a_full = bars;
-  auto bar_b_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto bar_b_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
-  auto bar_acc_full = [&](int b) { return bars + 8u * (1 + 2 * kStages + b); };
-  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 + 2 * kStages + b); };
-  __shared__ uint32_t s_tmem_base;
-  __shared__ int s_abort, s_skip;
-
-  // once any CTA of this launch has given up, the rest leave at once (uniformly per CTA)
-  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(a.error_flag);
-  __syncthreads();
-  if (s_skip) return;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int problem = blockIdx.y;
-  const int tile = blockIdx.x;
-  const int64_t tok_row0 = (int64_t)(problem / a.seg_per_group) * a.group_stride +
-                           (int64_t)(problem % a.seg_per_group) * a.n_tok + (int64_t)tile * kTileM;
-  const int cen_row0 = problem * a.n_cen;
-  const int n_tiles = (a.n_cen + kTileN - 1) / kTileN;
-
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    mbar_init(bar_a_full, 1);
-    for (int s = 0; s < kStages; ++s) { mbar_init(bar_b_full(s), 1); mbar_init(bar_b_empty(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 4); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
-                 "r"(kTmemCols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = s_tmem_base;
-  volatile int* abort_flag = &s_abort;
-
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar_a_full, 2 * kHalfBytes);
-      tma_load_2d(sA, &map_keys, bar_a_full, 0, (int)tok_row0);
-      tma_load_2d(sA + kHalfBytes, &map_keys, bar_a_full, 64, (int)tok_row0);
-      int issued = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % kStages;
-        if (!mbar_wait(bar_b_empty(s), ((j / kStages) & 1) ^ 1, abort_flag, 1)) break;
-        mbar_arrive_expect_tx(bar_b_full(s), 2 * kHalfBytes);
-        tma_load_2d(sB + s * 2 * kHalfBytes, &map_cent, bar_b_full(s), 0, cen_row0 + j * kTileN);
-        tma_load_2d(sB + s * 2 * kHalfBytes + kHalfBytes, &map_cent, bar_b_full(s), 64, cen_row0 + j * kTileN);
-        issued = j + 1;
-      }
-      if (*abort_flag) {
-        // give our own copies still in flight a bounded chance to land before the CTA exits
-        mbar_wait(bar_a_full, 0, abort_flag, 6);
-        for (int j = max(0, issued - kStages); j < issued; ++j)
-          mbar_wait(bar_b_full(j % kStages), (j / kStages) & 1, abort_flag, 7);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      bool ok = mbar_wait(bar_a_full, 0, abort_flag, 2);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j % kStages, buf = j & 1;
-        ok = mbar_wait(bar_b_full(s), (j / kStages) & 1, abort_flag, 3) &&
-             mbar_wait(bar_acc_empty(buf), ((j >> 1) & 1) ^ 1, abort_flag, 4);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * kTileN;
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t da = umma_desc_sw128(sA + kb * kHalfBytes);
-          const uint64_t db = umma_desc_sw128(sB + s * 2 * kHalfBytes + kb * kHalfBytes);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)   // K16 steps: 32 bytes along the swizzled row = +2 in the address field
-            tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, a.idesc, (kb | k) != 0);
-        }
-        tc_commit(bar_b_empty(s));     // the stage is free once these MMAs have read it
-        tc_commit(bar_acc_full(buf));  // and the accumulator is complete
-      }
-    }
-  } else {
-    // ---------------- epilogue: running arg-max over the centroid tiles ----------------
-    const int lane_group = warp & 3;                 // TMEM lanes 32*lane_group .. +31
-    const int row = lane_group * 32 + lane;
-    float best = -INFINITY;
-    int best_idx = 0;
-    bool ok = true;
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int buf = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(buf), (j >> 1) & 1, abort_flag, 5));   // warp-uniform
-      if (!ok) break;
-      tc_fence_after();
-      const int col0 = j * kTileN;
-      const int valid = min(kTileN, a.n_cen - col0);
-#pragma unroll 1
-      for (int ch = 0; ch < kTileN / 32; ++ch) {
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * kTileN + ch * 32, r);
-        tc_wait_ld();
-        tc_ld_landed(r);
-        if (ch * 32 + 32 <= valid) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[i]);
-            if (v > best) { best = v; best_idx = col0 + ch * 32 + i; }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = __uint_as_float(r[i]);
-            if (ch * 32 + i < valid && v > best) { best = v; best_idx = col0 + ch * 32 + i; }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
-    }
-    const int local_tok = tile * kTileM + row;
-    if (ok && local_tok < a.n_tok) a.assign[tok_row0 + row] = best_idx;
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && s_abort) *a.error_flag = s_abort;   // which wait gave up (see mbar_wait call sites)
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
-  }
-}
-
-// ---- assign, wide form ----------------------------------------------------------------------------
-// The form the build uses: a CTA works through consecutive 256-token blocks of one problem.  Per block
+// ---- assign kernel --------------------------------------------------------------------------------
+// A CTA works through consecutive 256-token blocks of one problem.  Per block
 // two 128-row token tiles (A, double-buffered per block) meet every centroid tile (B, streamed
 // through three stages) in two MMAs, so a centroid tile fetched into shared memory serves 256 tokens
 // and the CTA's set-up is paid once for many blocks; the accumulators fill all 512 TMEM columns
@@ -201,7 +52,8 @@ kmeans_assign_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_
 // epilogue warps (four per token tile, one per TMEM lane quarter) that keep the running arg-max
 // of their 32 tokens: per 32 columns a max tree, then the first column equal to the max (ties ->
 // lowest index, the rule of torch.argmax), so nothing in the epilogue is a serial chain.
-// Every mbarrier wait is bounded as in the narrow form above.
+// Every mbarrier wait has a time and an iteration limit; on expiry the CTA records where it gave up, releases its
+// TMEM and returns.
 constexpr int kWideThreads = 320;
 constexpr int kWideBStages = 3;
 constexpr uint32_t kWideTmemCols = 512;
@@ -768,18 +620,6 @@ int validate_fit(const ri_kmeans* p) {
   return RI_OK;
 }
 
-// With RI_KMEANS_TRACE=1 in the environment every launch is followed by a stream synchronise and a
-// line on stderr (debugging aid; never set it while capturing a graph).
-int trace_stage(const char* name, cudaStream_t s) {
-  static const bool on = getenv("RI_KMEANS_TRACE") != nullptr;
-  if (!on) return RI_OK;
-  const cudaError_t e = cudaStreamSynchronize(s);
-  fprintf(stderr, "[ri_kmeans] %s: %s\n", name, cudaGetErrorString(e));
-  fflush(stderr);
-  if (e != cudaSuccess) return ri_fail(RI_ERR_CUDA, "%s failed: %s", name, cudaGetErrorString(e));
-  return RI_OK;
-}
-
 template <int DT>
 int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStream_t s) {
   uint8_t* sc = static_cast<uint8_t*>(p->d_scratch);
@@ -792,21 +632,18 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
   int32_t* offset_work = reinterpret_cast<int32_t*>(sc + L.offset);
 
   RI_CUDA_OK(cudaMemsetAsync(err, 0, 4, s));
-  int rc0 = RI_OK;
   {
     const float step = (float)((double)N / (double)C);
     const float half = (float)((double)N / (double)C / 2.0);
     dim3 grid((C * 16 + 255) / 256, Z);
     init_centroids_kernel<<<grid, 256, 0, s>>>(static_cast<const uint4*>(centred), static_cast<uint4*>(cent), N, C, step, half);
     RI_LAUNCH_OK("init_centroids_kernel");
-    if ((rc0 = trace_stage("init_centroids", s)) != RI_OK) return rc0;
   }
   CUtensorMap map_keys, map_cent;
   int rc = make_row_map(&map_keys, centred, (int64_t)Z * N, DT);
   if (rc != RI_OK) return rc;
   rc = make_row_map(&map_cent, cent, (int64_t)Z * C, DT);
   if (rc != RI_OK) return rc;
-  RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAssignSmem));
   RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem));
 
   for (int it = 0; it < p->n_iters; ++it) {
@@ -818,14 +655,8 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
     AssignArgs aa;
     aa.assign = assign; aa.error_flag = err; aa.n_tok = n_tok; aa.n_cen = n_cen; aa.seg_per_group = seg;
     aa.group_stride = N;
-    aa.idesc = (1u << 4) | ((DT == RI_BF16 ? 1u : 0u) << 7) | ((DT == RI_BF16 ? 1u : 0u) << 10) |
-               ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-    static const bool narrow = getenv("RI_KMEANS_NARROW") != nullptr;   // the 128-token form (A/B timing)
-    if (narrow) {
-      dim3 agrid((n_tok + kTileM - 1) / kTileM, problems);
-      kmeans_assign_kernel<<<agrid, kAssignThreads, kAssignSmem, s>>>(map_keys, map_cent, aa);
-      RI_LAUNCH_OK("kmeans_assign_kernel");
-    } else {
+    aa.idesc = idesc_f16(DT, kTileM, kTileN);
+    {
       // blocks per CTA: enough CTAs for about a dozen waves over the SMs, at most 16 blocks each
       WideArgs wa;
       wa.a = aa;
@@ -837,7 +668,6 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
       kmeans_assign_wide_kernel<<<wgrid, kWideThreads, kWideSmem, s>>>(map_keys, map_cent, wa);
       RI_LAUNCH_OK("kmeans_assign_wide_kernel");
     }
-    if ((rc0 = trace_stage("assign", s)) != RI_OK) return rc0;
 
     BucketArgs ba;
     ba.assign = assign; ba.order = order;
@@ -853,7 +683,6 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
       RI_CUDA_OK(cudaFuncSetAttribute(kmeans_bucket_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bsmem));
     kmeans_bucket_kernel<<<problems, 1024, bsmem, s>>>(ba, workers);
     RI_LAUNCH_OK("kmeans_bucket_kernel");
-    if ((rc0 = trace_stage("bucket", s)) != RI_OK) return rc0;
 
     UpdateArgs ua = {};
     ua.centred = static_cast<const uint2*>(centred);
@@ -891,7 +720,6 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
     if (form) kmeans_update_kernel<DT, true><<<ugrid, 256, 0, s>>>(ua, problems);
     else kmeans_update_kernel<DT, false><<<ugrid, 256, 0, s>>>(ua, problems);
     RI_LAUNCH_OK("kmeans_update_kernel");
-    if ((rc0 = trace_stage("update", s)) != RI_OK) return rc0;
   }
   if (!p->center)
     RI_CUDA_OK(cudaMemcpyAsync(p->d_centroids, cent, (size_t)Z * C * 256, cudaMemcpyDeviceToDevice, s));

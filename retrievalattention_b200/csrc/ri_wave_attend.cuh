@@ -518,6 +518,7 @@ inline void fill_attend_args(const ri_wave_layer& p, const Layout& L, const Exec
     a.n_exact = eb->lengths;
     a.static_len = nullptr;
     a.rows = nullptr;
+    a.lse_out = eb->lse_out;
   }
 }
 

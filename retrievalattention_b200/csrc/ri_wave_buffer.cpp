@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <condition_variable>
 #include <cstdio>
+#include <cstring>
 #include <functional>
 #include <list>
 #include <mutex>
@@ -290,6 +291,40 @@ extern "C" int ri_wb_batch_access(ri_wave_buffer* wb) {
   int n = 0;
   for (uint8_t o : wb->overflowed) n += o;
   return n;   // number of groups whose retrieval was cut by the page budget (the reference prints a warning)
+}
+
+// After ri_wb_batch_access: the worker threads copy every missed page of every group from the cluster store in host
+// memory into a staging area in host memory, group g's pages back to back from row 0 of its slot (page j at row
+// miss_cumsum[g][j]) — the layout gather_copy_and_concat reads when it is given miss_cumsum as the source offsets.
+// Blocks until the copies are done; *max_rows_out = the largest number of staged rows of any group.
+extern "C" int ri_wb_stage_misses(ri_wave_buffer* wb, const void* h_src_keys, const void* h_src_values,
+                                  int64_t src_rows_per_group, void* h_stage_keys, void* h_stage_values,
+                                  int64_t stage_rows_per_group, int32_t row_bytes, int32_t* max_rows_out) {
+  if (!wb || !wb->miss_ids || !h_src_keys || !h_src_values || !h_stage_keys || !h_stage_values || !max_rows_out)
+    return ri_fail(RI_ERR_INVALID, "ri_wb_stage_misses: null pointer");
+  if (row_bytes <= 0 || src_rows_per_group <= 0 || stage_rows_per_group <= 0)
+    return ri_fail(RI_ERR_INVALID, "ri_wb_stage_misses: bad sizes");
+  const int64_t bs = wb->buffer_pages;
+  std::vector<int> rows(wb->groups, 0);
+  int* rows_p = rows.data();
+  const char *sk = static_cast<const char*>(h_src_keys), *sv = static_cast<const char*>(h_src_values);
+  char *dk = static_cast<char*>(h_stage_keys), *dv = static_cast<char*>(h_stage_values);
+  wb->for_groups([=](int g) {
+    const int n = wb->miss_n[g];
+    int total = 0;
+    for (int j = 0; j < n; ++j) {
+      const int64_t src = wb->miss_ids[g * bs + j], dst = wb->miss_cum[g * bs + j];
+      const int sz = wb->miss_sizes[g * bs + j];
+      if (src < 0 || src + sz > src_rows_per_group || dst < 0 || dst + sz > stage_rows_per_group) continue;   // never copy outside
+      memcpy(dk + (g * stage_rows_per_group + dst) * row_bytes, sk + (g * src_rows_per_group + src) * row_bytes, (size_t)sz * row_bytes);
+      memcpy(dv + (g * stage_rows_per_group + dst) * row_bytes, sv + (g * src_rows_per_group + src) * row_bytes, (size_t)sz * row_bytes);
+      total = std::max(total, (int)(dst + sz));
+    }
+    rows_p[g] = total;
+  });
+  wb->pool.wait();
+  *max_rows_out = *std::max_element(rows.begin(), rows.end());
+  return RI_OK;
 }
 
 extern "C" int ri_wb_sync(ri_wave_buffer* wb) {

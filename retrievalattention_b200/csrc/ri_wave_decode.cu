@@ -146,7 +146,18 @@ extern "C" int ri_wave_attend_buffer(const ri_wave_layer* p, const void* d_exec_
   RI_REQUIRE(d_exec_keys && d_exec_values && d_valid_lengths && exec_stride > 0, "ri_wave_attend_buffer: bad buffer");
   RI_REQUIRE(((uintptr_t)d_exec_keys | (uintptr_t)d_exec_values) % 16 == 0, "execution buffers must be 16-byte aligned");
   const Layout L = make_layout(*p);
-  const ExecBuffer eb = {d_exec_keys, d_exec_values, exec_stride, d_valid_lengths};
+  const ExecBuffer eb = {d_exec_keys, d_exec_values, exec_stride, d_valid_lengths, nullptr};
+  return launch_attend(*p, L, static_cast<cudaStream_t>(stream), &eb);
+}
+
+extern "C" int ri_wave_attend_buffer_lse(const ri_wave_layer* p, const void* d_exec_keys, const void* d_exec_values,
+                                         int32_t exec_stride, const int32_t* d_valid_lengths, float* d_lse_out, void* stream) {
+  int rc = validate(p);
+  if (rc != RI_OK) return rc;
+  RI_REQUIRE(d_exec_keys && d_exec_values && d_valid_lengths && d_lse_out && exec_stride > 0, "ri_wave_attend_buffer_lse: bad buffer");
+  RI_REQUIRE(((uintptr_t)d_exec_keys | (uintptr_t)d_exec_values) % 16 == 0, "execution buffers must be 16-byte aligned");
+  const Layout L = make_layout(*p);
+  const ExecBuffer eb = {d_exec_keys, d_exec_values, exec_stride, d_valid_lengths, d_lse_out};
   return launch_attend(*p, L, static_cast<cudaStream_t>(stream), &eb);
 }
 

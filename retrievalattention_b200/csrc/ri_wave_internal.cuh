@@ -52,7 +52,7 @@ inline Layout make_layout(const ri_wave_layer& p) {
 int launch_scan(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 int launch_select(const ri_wave_layer& p, const Layout& L, cudaStream_t s);
 // `eb` (optional): attend over a dense execution buffer instead of the cluster-contiguous store.
-struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; };
+struct ExecBuffer { const void* keys; const void* values; int64_t stride; const int32_t* lengths; float* lse_out; };
 // `gather` (optional): also store the output into every rank's gather buffer (several GPUs).
 int launch_attend(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ExecBuffer* eb = nullptr,
                   const ri_wave_gather* gather = nullptr);

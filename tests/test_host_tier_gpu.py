@@ -13,13 +13,14 @@ from retrievalattention_b200.synthetic import make_kv, make_queries
 pytestmark = pytest.mark.gpu
 
 
-def build(kv_on_host, batch, layers, kv_heads, q_heads, seq_len, max_new):
+def build(kv_on_host, batch, layers, kv_heads, q_heads, seq_len, max_new, stage_misses=True):
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
     cfg = generate_config(seq_len, 0.05, 0.2, n_segments=2)
     mapping = {str(l): "cuda:0" for l in range(layers)}
     cache = retroinfer_cache([0] * batch, layers, batch, seq_len + max_new, kv_heads, q_heads, 128, torch.bfloat16,
-                             mapping, max_new, num_gpus=1, model_size=8, kv_on_host=kv_on_host, **cfg.as_kwargs())
+                             mapping, max_new, num_gpus=1, model_size=8, kv_on_host=kv_on_host, stage_misses=stage_misses,
+                             **cfg.as_kwargs())
     for b in range(batch):
         for l in range(layers):
             k, v = make_kv(kv_heads, seq_len, 128, seed=100 * l + b, device="cuda")
@@ -29,9 +30,12 @@ def build(kv_on_host, batch, layers, kv_heads, q_heads, seq_len, max_new):
     return cache, cfg
 
 
-def test_host_tier_matches_oracle_and_hbm_tier():
+# staged: missed pages copied by the host's worker threads into a pinned staging area and sent up on a side stream while
+# the first attention pass runs; uva: the reference's pattern (the copy kernel reads them from pinned memory itself)
+@pytest.mark.parametrize("stage_misses", [True, False], ids=["staged", "uva"])
+def test_host_tier_matches_oracle_and_hbm_tier(stage_misses):
     batch, layers, kv_heads, q_heads, seq_len, max_new = 2, 2, 2, 8, 2048 + 68, 8
-    host, cfg = build(True, batch, layers, kv_heads, q_heads, seq_len, max_new)
+    host, cfg = build(True, batch, layers, kv_heads, q_heads, seq_len, max_new, stage_misses)
     hbm, _ = build(False, batch, layers, kv_heads, q_heads, seq_len, max_new)
     g = batch * kv_heads
     for l in range(layers):   # same index, same cluster-contiguous rows, different memory
