@@ -934,6 +934,8 @@ def main():
     ap.add_argument("--no-cfg4", action="store_true",
                     help="several GPUs: skip the run of configuration 4 (72B geometry, heads sharded) after the main one")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
+    ap.add_argument("--prefill-seq", type=int, default=0,
+                    help="only the dense prefill attention of one prompt of this many tokens (profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -947,6 +949,10 @@ def main():
     if args.impl == "reference":
         if rank == 0:
             reference_arm(geo, args, log)
+        return
+    if args.prefill_seq:
+        if rank == 0:
+            print(json.dumps({"prefill_attn": prefill_summary(geo, log, args.prefill_seq)}), flush=True)
         return
     if args.config == "cfg2":
         if rank == 0:

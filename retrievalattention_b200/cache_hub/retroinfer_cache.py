@@ -225,20 +225,38 @@ class retroinfer_cache(KV_Cache):
         self.cluster_count[layer_idx][rows].copy_(r["cluster_count"])
         self.cluster_offset[layer_idx][rows].copy_(r["cluster_offset"])
         self.centroids_mask[layer_idx][rows].copy_(r["cluster_count"] == 0)
-        self.list_keys[layer_idx][batch_idx, :, :valid_length].copy_(r["keys"], non_blocking=self.kv_on_host)
-        self.list_values[layer_idx][batch_idx, :, :valid_length].copy_(r["values"], non_blocking=self.kv_on_host)
         self._error_flags.append(r["error"])
         if self.kv_on_host:
-            self._keep_alive.append(r)            # sources of the asynchronous device-to-host copies
+            # the offload of this request-layer's laid-out rows runs on a side stream, under the clustering of the next
+            # request-layer (the reference's offload <-> k-means overlap, :388-403); at most two laid-out copies are
+            # kept on the device
+            dev = key_states.device
+            per = self._per_device[self.layer_mapping[str(layer_idx)]]
+            if "offload_stream" not in per:
+                per["offload_stream"] = torch.cuda.Stream(device=dev)
+            off, done = per["offload_stream"], torch.cuda.Event()
+            off.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(off):
+                for h in range(self.kv_head):      # one contiguous run per head: a plain asynchronous copy each
+                    self.list_keys[layer_idx][batch_idx, h, :valid_length].copy_(r["keys"][h], non_blocking=True)
+                    self.list_values[layer_idx][batch_idx, h, :valid_length].copy_(r["values"][h], non_blocking=True)
+                done.record(off)
+            self._keep_alive.append((done, r))
+            while len(self._keep_alive) > 2:
+                self._keep_alive.pop(0)[0].synchronize()
             self.wave_buffer[layer_idx].async_construction(None, r["cluster_count"], batch_idx)
+        else:
+            self.list_keys[layer_idx][batch_idx, :, :valid_length].copy_(r["keys"])
+            self.list_values[layer_idx][batch_idx, :, :valid_length].copy_(r["values"])
 
         if layer_idx == self.layer_num - 1 and batch_idx + bsz == self.batch_size:
             self.context += seq_len
         return key_states[:, vs:], value_states[:, vs:]
 
     def sync(self, layer_idx, batch_idx):
-        """The reference waits here for its host offload and starts the CPU re-layout (:443-458);
-        the layout was already written by the clustering pass, so there is nothing to wait for."""
+        """The reference waits here for its host offload and starts the CPU re-layout (:443-458).  The layout was
+        already written by the clustering pass; the host tier's offload copies keep running on their side stream and
+        ``prepare_cache`` waits for the last of them."""
         return None
 
     def prepare_cache(self):
