@@ -688,62 +688,78 @@ def run_host_tier(geo, args, log):
     on the GPU (the reference's tiers), ``--layers`` of its layers (pinned memory is the limit), eager stepping (the host
     takes part in every layer).  Two query streams: fresh Gaussian queries every step (no temporal locality: the worst
     case for the page cache) and slowly drifting ones (q_t = 0.95 q_{t-1} + 0.31 noise).  Reports tokens/s, the page
-    cache's hit rate and the host-to-device bytes of the missed pages per second."""
+    cache's hit rate and the host-to-device bytes of the missed pages per second, for every way of bringing the missed
+    pages up (``--miss-path`` picks one): the side-stream pull with the next layer searched and pulled one layer ahead
+    (the next layer's query handed over as ``queries_next``: the best any estimate can do), the same without looking
+    ahead, the host-staged copy, and the reference's own pattern."""
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     cfg = geo.index()
     steps, warm = args.steps, max(args.warmup, 3)
-    max_new = 2 * (steps + warm) + 4
+    max_new = 8 * (steps + warm) + 4
     mapping = {str(l): str(device) for l in range(geo.layers)}
-    cache = retroinfer_cache([0] * geo.batch, geo.layers, geo.batch, geo.context + max_new, geo.kv_heads, geo.q_heads, 128,
-                             torch.bfloat16, mapping, max_new, num_gpus=1, model_size=8, kv_on_host=True,
-                             stage_misses=not args.uva_misses, **cfg.as_kwargs())
-    for l in range(geo.layers):
-        for b in range(geo.batch):
-            k, v = make_kv(geo.kv_heads, geo.context, 128, seed=l * 1000 + b, theta=geo.rope_theta, device=device)
-            cache.prefill_update_kv_cache(None, k, v, l, b)
-        log(f"set-up: layer {l + 1}/{geo.layers} indexed")
-    cache.prepare_cache()
-    g = torch.Generator(device=device).manual_seed(5)
-    rnd = lambda h: torch.randn((geo.batch, 1, h, 128), generator=g, device=device).to(torch.bfloat16)   # noqa: E731
-    results = {}
-    for name, keep in (("fresh queries", 0.0), ("drifting queries", 0.95)):
-        q = [rnd(geo.q_heads).float() for _ in range(geo.layers)]
-        pages = [0, 0]
-
-        def step(count):
+    modes = {"pull, one layer ahead": ("pull", True), "pull": ("pull", False), "staged": ("staged", False),
+             "uva (the reference's pattern)": ("uva", False)}
+    if args.miss_path:
+        modes = {k: v for k, v in modes.items() if v[0] == args.miss_path}
+    results, cache, built = {}, None, None
+    for mode, (path, ahead) in modes.items():
+        if built != path:
+            cache = None
+            torch.cuda.empty_cache()
+            cache = retroinfer_cache([0] * geo.batch, geo.layers, geo.batch, geo.context + max_new, geo.kv_heads, geo.q_heads,
+                                     128, torch.bfloat16, mapping, max_new, num_gpus=1, model_size=8, kv_on_host=True,
+                                     miss_path=path, use_cluster_estimation=path == "pull", **cfg.as_kwargs())
             for l in range(geo.layers):
-                q[l] = keep * q[l] + (1 - keep * keep) ** 0.5 * rnd(geo.q_heads).float()
-                cache.decode_update_kv_cache(rnd(geo.kv_heads), rnd(geo.kv_heads), l)
-                cache.compute(q[l].to(torch.bfloat16), l)
-                if count:
-                    pages[0] += int(cache.page_lists[l][3].sum())
-                    pages[1] += int(cache.page_lists[l][7].sum())
-        for _ in range(warm):
-            step(False)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            step(True)
-        torch.cuda.synchronize()
-        sec = time.perf_counter() - t0
-        hit, miss = pages
-        results[name] = {"tok_s": round(geo.batch * steps / sec, 1), "ms_per_step": round(sec / steps * 1e3, 3),
-                         "page_hit_rate": round(hit / max(hit + miss, 1), 4),
-                         "missed_page_gbs": round(miss * 8 * 128 * 2 * 2 / sec / 1e9, 2)}
-        log(f"{name}: {results[name]}")
-    main = results["drifting queries"]
+                for b in range(geo.batch):
+                    k, v = make_kv(geo.kv_heads, geo.context, 128, seed=l * 1000 + b, theta=geo.rope_theta, device=device)
+                    cache.prefill_update_kv_cache(None, k, v, l, b)
+            cache.prepare_cache()
+            built = path
+            log(f"set-up: {geo.layers} layers indexed, miss path {path}")
+        g = torch.Generator(device=device).manual_seed(5)
+        rnd = lambda h: torch.randn((geo.batch, 1, h, 128), generator=g, device=device).to(torch.bfloat16)   # noqa: E731
+        results[mode] = {}
+        for name, keep in (("fresh queries", 0.0), ("drifting queries", 0.95)):
+            q = [rnd(geo.q_heads).float() for _ in range(geo.layers)]
+            pages = [0, 0]
+
+            def step(count):
+                qs = []
+                for l in range(geo.layers):
+                    q[l] = keep * q[l] + (1 - keep * keep) ** 0.5 * rnd(geo.q_heads).float()
+                    qs.append(q[l].to(torch.bfloat16))
+                for l in range(geo.layers):
+                    cache.decode_update_kv_cache(rnd(geo.kv_heads), rnd(geo.kv_heads), l)
+                    cache.compute(qs[l], l, qs[l + 1] if ahead and l + 1 < geo.layers else None)
+                    if count:
+                        pages[0] += int(cache.page_lists[l][3].sum())
+                        pages[1] += int(cache.page_lists[l][7].sum())
+            for _ in range(warm):
+                step(False)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                step(True)
+            torch.cuda.synchronize()
+            sec = time.perf_counter() - t0
+            hit, miss = pages
+            results[mode][name] = {"tok_s": round(geo.batch * steps / sec, 1), "ms_per_step": round(sec / steps * 1e3, 3),
+                                   "ms_per_layer": round(sec / steps / geo.layers * 1e3, 3),
+                                   "page_hit_rate": round(hit / max(hit + miss, 1), 4),
+                                   "missed_page_gbs": round(miss * 8 * 128 * 2 * 2 / sec / 1e9, 2)}
+            log(f"{mode}, {name}: {results[mode][name]}")
+    first = next(iter(results))
+    main = results[first]["drifting queries"]
     print(json.dumps({
         "metric": METRIC, "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": f"{geo.name}: host tier (cluster store in pinned host memory, GPU page cache of "
                                f"{cfg.cache_cluster_num} clusters per group), {geo.layers} layers, batch {geo.batch}, ctx {geo.context}, "
-                               f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; missed pages "
-                               + ("read through UVA by the copy kernel" if args.uva_misses else
-                                  "staged by host threads, one strided copy per tensor and layer on a side stream"),
+                               f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; value: drifting queries, missed pages by '{first}'",
                    "timing": "wall clock around eager steps (the host takes part in every layer)"},
         "host_tier": results}), flush=True)
 
@@ -929,8 +945,8 @@ def main():
     ap.add_argument("--no-kmeans", action="store_true", help="skip the short clustering run (key kmeans, single GPU)")
     ap.add_argument("--kv-on-host", action="store_true",
                     help="time the host tier of --config (cluster store in pinned host memory, GPU page cache), --layers layers")
-    ap.add_argument("--uva-misses", action="store_true",
-                    help="with --kv-on-host: the reference's pattern (the copy kernel reads missed pages through UVA)")
+    ap.add_argument("--miss-path", default="", choices=["", "pull", "staged", "uva"],
+                    help="with --kv-on-host: only this way of bringing missed pages up (default: all, one after the other)")
     ap.add_argument("--no-cfg4", action="store_true",
                     help="several GPUs: skip the run of configuration 4 (72B geometry, heads sharded) after the main one")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")

@@ -15,27 +15,34 @@ offload, no CPU re-layout).  Two storage tiers:
 * ``kv_on_host=True`` (not a reference argument): the reference's tiers — cluster-contiguous KV
   in pinned host memory (:264-274), an LRU page cache of ``cache_cluster_num`` clusters on the GPU
   (:204-211), a host-side wave buffer per layer (:117-121) and an execution buffer assembled per step
-  (:642-648).  Per layer: scan + select on the GPU, the select stage writes the retrieved ids straight into
-  pinned host memory and the host waits on an event (instead of the blocking copy of :575); while the host
-  walks the LRU lists and its worker threads copy the missed pages into a pinned staging area, the GPU already
-  attends the estimation zone and the steady zone; the staged pages go up with one strided copy per tensor
-  on a side stream; behind that copy's event ``gather_copy_and_concat`` appends missed and hit pages to the
-  execution buffer, the second attention pass covers them and merges by log-sum-exp, and
-  ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
-  ``stage_misses=False`` keeps the reference's own pattern (the copy kernel reads the missed pages from pinned
-  memory through UVA, one attention pass).
+  (:642-648).  Three ways to bring the missed pages up (``miss_path``):
+
+  - ``"pull"`` (default): the select stage writes the retrieved ids straight into pinned host memory and the host
+    waits on an event (instead of the blocking copy of :575); while the host walks the LRU lists the GPU already
+    attends the estimation zone and the steady zone; then ``gather_copy_and_concat`` runs on a SIDE stream and
+    reads the missed pages from the pinned store itself (over PCIe) into one of two execution buffers, hit pages
+    behind them; behind that kernel's event the second attention pass covers the pages and merges with the
+    first by log-sum-exp; ``gather_copy_and_scatter`` admits the missed pages into the GPU cache (:682-690).
+    With ``use_cluster_estimation=True`` the search, the list walk and the pull of layer l+1 are started inside
+    layer l's call with ``queries_next``, so a layer's pages cross PCIe under the previous layer's work.
+  - ``"staged"``: the host's worker threads copy the missed pages into a pinned staging area and one strided
+    ``cudaMemcpy2DAsync`` per tensor sends them up on the side stream (measured slower: a second pass over
+    the bytes on the host).
+  - ``"uva"``: the reference's own pattern — blocking id copy, one copy kernel on the main stream, one
+    attention pass, three host waits.
 
 After every 1024 generated tokens ``decode_update_kv_cache`` folds them into the index (``_update_kv_cache``,
 :462-524), provided ``max_new_length`` announced that many at construction.
 
-``use_cluster_estimation=True`` (HBM tier): ``compute(queries, l, queries_next)`` also searches layer ``l + 1``'s
+``use_cluster_estimation=True``: ``compute(queries, l, queries_next)`` also searches layer ``l + 1``'s
 clusters with ``queries_next`` (the caller's estimate of the next layer's query, model_hub/LLM.py:102-107), and a
 layer whose clusters were searched ahead in this step attends those clusters with its real query instead of
 searching again (:565, :582-595).  Layers without a search made for them (the first ones, or whenever the caller
 passes no ``queries_next``) search with their own query — the reference instead reuses whatever an earlier step
 left in its index buffer for layer 2, an off-by-one that is not reproduced.  The point of the feature in the
-reference is to start the host wave buffer's work one layer early; with the cluster store in HBM there is nothing
-to hide, so this mode exists for its results (it is slower than the single kernel: five launches per layer).
+reference is to start the host wave buffer's work one layer early, which is what the host tier's ``"pull"`` path
+does with it; with the cluster store in HBM there is nothing to hide, so there the mode exists for its results
+(it is slower than the single kernel: five launches per layer).
 """
 from __future__ import annotations
 
@@ -56,7 +63,7 @@ class retroinfer_cache(KV_Cache):
                  static_pattern_start: int, static_pattern_end: int, core: int, n_centroids: int, n_segment: int,
                  nprobe: int, max_compute_cluster_num: int, cache_unit_size: int, cache_cluster_num: int,
                  num_gpus: int, model_size: int, use_cluster_estimation: bool = False,
-                 kv_on_host: bool = False, fuse_append: bool = True, stage_misses: bool = True) -> None:
+                 kv_on_host: bool = False, fuse_append: bool = True, miss_path: str = "pull") -> None:
         super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
                          layer_mapping, num_gpus, model_size)
         if head_dim != 128:
@@ -96,7 +103,10 @@ class retroinfer_cache(KV_Cache):
         self.list_stride = self.input_length - self.static_pattern_total + self.input_length_new
 
         self.kv_on_host = bool(kv_on_host)
-        self.stage_misses = bool(stage_misses) and self.kv_on_host
+        if miss_path not in ("pull", "staged", "uva"):
+            raise ValueError(f"miss_path must be 'pull', 'staged' or 'uva', got {miss_path!r}")
+        self.miss_path = miss_path if self.kv_on_host else None
+        self.stage_misses = self.miss_path == "staged"
         g, c, d = self.batch_groups, n_centroids, head_dim
         self.steady_zone_keys, self.steady_zone_values = [], []
         self.centroids, self.value_sum, self.cluster_size = [], [], []
@@ -138,8 +148,8 @@ class retroinfer_cache(KV_Cache):
         # use_cluster_estimation: a search made one layer ahead lives in the layer's own scratch until it is used
         self._ahead = [False] * layer_num
         if self.use_cluster_estimation:
-            if kv_on_host:
-                raise NotImplementedError("use_cluster_estimation is built for the HBM tier (kv_on_host=False)")
+            if kv_on_host and miss_path != "pull":
+                raise NotImplementedError("on the host tier use_cluster_estimation needs miss_path='pull'")
             for dev in self._per_device:
                 self._per_device[dev]["layer_scratch"] = {}
         if self.kv_on_host:
@@ -179,6 +189,19 @@ class retroinfer_cache(KV_Cache):
             per["exec_keys"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
             per["exec_values"] = torch.zeros((g, self.execution_stride, d), dtype=self.dtype, device=dev)
             per["valid_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+            if self.miss_path in ("pull", "staged"):
+                per["copy_stream"] = torch.cuda.Stream(device=dev)
+                per["lse"] = torch.zeros((g, self.group_size), dtype=torch.float32, device=dev)
+                per["part"] = torch.zeros((g, self.group_size, d), dtype=self.dtype, device=dev)
+                per["steady_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
+            if self.miss_path == "pull":
+                # two execution buffers used by even and odd layers (a layer's pages may arrive while the layer
+                # before it still reads its own), each with its page-row counts and two events
+                per["exec"] = [(per["exec_keys"], per["exec_values"]),
+                               (torch.zeros_like(per["exec_keys"]), torch.zeros_like(per["exec_values"]))]
+                per["rest_lengths"] = [torch.zeros((g,), dtype=torch.int32, device=dev) for _ in range(2)]
+                per["selected"] = [torch.cuda.Event() for _ in range(2)]
+                per["pulled"] = [torch.cuda.Event() for _ in range(2)]
             if self.stage_misses:
                 # two staging areas used alternately (the host refills one while the other's copy may still be running),
                 # on the host (pinned) and on the device; one side stream and one event per area
@@ -188,12 +211,8 @@ class retroinfer_cache(KV_Cache):
                                      for _ in range(2)]
                 per["stage_dev"] = [tuple(torch.zeros((g, rows, d), dtype=self.dtype, device=dev) for _ in range(2))
                                     for _ in range(2)]
-                per["copy_stream"] = torch.cuda.Stream(device=dev)
                 per["uploaded"] = [torch.cuda.Event() for _ in range(2)]
                 per["selected"] = torch.cuda.Event()
-                per["lse"] = torch.zeros((g, self.group_size), dtype=torch.float32, device=dev)
-                per["part"] = torch.zeros((g, self.group_size, d), dtype=self.dtype, device=dev)
-                per["steady_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
                 per["rest_lengths"] = torch.zeros((g,), dtype=torch.int32, device=dev)
                 per["turn"] = 0
         self._keep_alive = []
@@ -288,7 +307,7 @@ class retroinfer_cache(KV_Cache):
                 steady_keys=self.steady_zone_keys[ldx].view(g, self.static_stride, self.head_dim),
                 steady_values=self.steady_zone_values[ldx].view(g, self.static_stride, self.head_dim),
                 static_len=per["static_len"], scratch=self._scratch_for(ldx, per))
-            if self.stage_misses:
+            if self.miss_path in ("pull", "staged"):
                 # the select stage stores the ranked ids straight into the pinned array the host wave buffer reads
                 self._layers[ldx].retrieved_ids = self.cluster_ids[ldx]
                 self._layers[ldx].params.d_retrieved_ids = self.cluster_ids[ldx].data_ptr()
@@ -394,7 +413,10 @@ class retroinfer_cache(KV_Cache):
         if self.kv_on_host:
             if gather is not None:
                 raise NotImplementedError("the peer-store gather is built for the HBM tier only")
-            out = self._compute_host_tier(queries.contiguous(), layer_idx, out)
+            if self.miss_path == "pull":
+                out = self._compute_host_tier_pull(queries.contiguous(), layer_idx, queries_next, out)
+            else:
+                out = self._compute_host_tier(queries.contiguous(), layer_idx, out)
         elif self.use_cluster_estimation:
             if gather is not None:
                 raise NotImplementedError("the peer-store gather is not combined with use_cluster_estimation")
@@ -530,6 +552,105 @@ class retroinfer_cache(KV_Cache):
         gather_copy_and_scatter(ek, self.cache_keys[layer_idx], ev, self.cache_values[layer_idx], upd_buf, upd_sizes,
                                 upd_cache, upd_n, g, self.execution_stride, self.cache_size, self.buffer_size, static_len)
         return out
+
+    def _compute_host_tier_pull(self, queries, layer_idx, queries_next, out):
+        """One host-tier layer with the missed pages pulled over PCIe by a copy kernel on a side stream.
+
+        First pass (main stream): estimation zone + steady zone, with its log-sum-exp.  Second pass, behind the
+        pull's event: the retrieved pages, merged with the first.  With ``use_cluster_estimation`` and a
+        ``queries_next`` the NEXT layer's search is enqueued in front of this layer's own work and its list walk and
+        pull are started before this call returns: the host walks the lists while the GPU attends this layer, and the
+        next layer's pages cross PCIe under this layer's second pass and the next layer's first."""
+        import ctypes as C
+
+        from .. import _lib
+        from ..kernels import gather_copy_and_scatter
+
+        layer, wb = self._layers[layer_idx], self.wave_buffer[layer_idx]
+        dev = self.layer_mapping[str(layer_idx)]
+        per = self._per_device[dev]
+        g, d, gs = self.batch_groups, self.head_dim, self.group_size
+        main = torch.cuda.current_stream(dev)
+        if out is None:
+            out = torch.empty_like(queries)
+        static_len = self.static_pattern_total if layer_idx == self.layer_num - 1 else self.static_pattern_total + 1
+        par = layer_idx & 1
+        # 1. searches first: the host needs their ids soonest.  The next layer's (with the caller's estimate of its
+        #    query), then this layer's own unless it was searched one layer ahead
+        ahead = (self.use_cluster_estimation and queries_next is not None and layer_idx + 1 < self.layer_num
+                 and self.layer_mapping[str(layer_idx + 1)] == dev)
+        if ahead:
+            self._q_next_alive = queries_next.contiguous()
+            self._search(layer_idx + 1, self._q_next_alive, par ^ 1)
+        searched_before = self._ahead[layer_idx]
+        if searched_before:
+            self._ahead[layer_idx] = False
+            layer.stage("rescore", queries, out)          # the estimation entries' scores for the real query
+        else:
+            self._search(layer_idx, queries, par)
+        # 2. nothing of this needs a page: estimation zone + steady zone, read where they lie
+        per["steady_lengths"].fill_(static_len)
+        layer._bind(queries, per["part"].view_as(queries))
+        _lib.check(_lib.lib.ri_wave_attend_buffer_lse(
+            C.byref(layer.params), self.steady_zone_keys[layer_idx].data_ptr(), self.steady_zone_values[layer_idx].data_ptr(),
+            self.static_stride, per["steady_lengths"].data_ptr(), per["lse"].data_ptr(), _lib.current_stream()),
+            "ri_wave_attend_buffer_lse")
+        if not searched_before:
+            self._lists_and_pull(layer_idx, par)          # the host walks the lists while the first pass runs
+        # 3. behind the pull: the second pass over the pages, merged with the first by log-sum-exp
+        ek, ev = per["exec"][par]
+        rest = per["rest_lengths"][par]
+        main.wait_event(per["pulled"][par])
+        _lib.check(_lib.lib.ri_weighted_flash_decoding(
+            queries.data_ptr(), ek.data_ptr(), ev.data_ptr(), None, rest.data_ptr(), per["part"].data_ptr(),
+            per["lse"].data_ptr(), out.data_ptr(), None, g, gs, self.execution_stride, _lib.dtype_code(self.dtype),
+            _lib.current_stream()), "ri_weighted_flash_decoding")
+        torch.add(rest, static_len, out=per["valid_lengths"])
+        if ahead:
+            self._lists_and_pull(layer_idx + 1, par ^ 1)
+            self._ahead[layer_idx + 1] = True
+        # 4. admit the missed pages (they lie in the execution buffer from row 0)
+        upd_buf, upd_sizes, upd_cache, upd_n = self.page_lists[layer_idx][8:12]
+        wb.sync()                                     # update lists are final (:682)
+        gather_copy_and_scatter(ek, self.cache_keys[layer_idx], ev, self.cache_values[layer_idx], upd_buf, upd_sizes,
+                                upd_cache, upd_n, g, self.execution_stride, self.cache_size, self.buffer_size, 0)
+        return out
+
+    def _search(self, layer_idx, q, par):
+        """scan + select of one layer on the main stream; the ranked ids land in pinned memory."""
+        layer = self._layers[layer_idx]
+        per = self._per_device[self.layer_mapping[str(layer_idx)]]
+        sink = per["part"].view_as(q)                 # the stages take an output pointer; these two do not write it
+        layer.stage("scan", q, sink)
+        layer.stage("select", q, sink)
+        per["selected"][par].record(torch.cuda.current_stream(sink.device))
+
+    def _lists_and_pull(self, layer_idx, par):
+        """Host: wait for the ids, walk the LRU lists.  Side stream: missed pages from the pinned store (read by the
+        copy kernel over PCIe) and hit pages from the GPU cache into execution buffer ``par`` from row 0."""
+        from ..kernels import gather_copy_and_concat
+
+        wb = self.wave_buffer[layer_idx]
+        dev = self.layer_mapping[str(layer_idx)]
+        per = self._per_device[dev]
+        g, d = self.batch_groups, self.head_dim
+        per["selected"][par].synchronize()
+        wb.batch_access()
+        (hit_ids, hit_sizes, hit_cum, hit_n, miss_ids, miss_sizes, miss_cum, miss_n) = self.page_lists[layer_idx][:8]
+        ek, ev = per["exec"][par]
+        side = per["copy_stream"]
+        # this buffer's readers of two layers ago were enqueued before the search whose event this is
+        side.wait_event(per["selected"][par])
+        sk = self.steady_zone_keys[layer_idx].view(g, self.static_stride, d)
+        sv = self.steady_zone_values[layer_idx].view(g, self.static_stride, d)
+        lk = self.list_keys[layer_idx].view(g, self.list_stride, d)
+        lv = self.list_values[layer_idx].view(g, self.list_stride, d)
+        with torch.cuda.stream(side):
+            gather_copy_and_concat(sk, lk, self.cache_keys[layer_idx], ek, sv, lv, self.cache_values[layer_idx], ev,
+                                   miss_ids, miss_sizes, miss_cum, miss_n, hit_ids, hit_sizes, hit_cum, hit_n,
+                                   per["rest_lengths"][par], g, self.static_stride, self.list_stride, self.cache_size,
+                                   self.execution_stride, self.buffer_size, 0)
+        per["pulled"][par].record(side)
 
     def _zero_counts(self, dev, g):
         per = self._per_device[dev]

@@ -36,6 +36,7 @@ struct ConcatArgs {
   int32_t* valid;
   int64_t len1, len2, len3_units, buffer_rows;
   int index_length, copy_rows1;
+  int ctas2;       // CTAs per group that move units of src2
 };
 
 // dst rows = src1[:copy_rows1] ++ listed units of src2 (vector-level start index) ++ listed units of
@@ -48,39 +49,35 @@ __global__ void __launch_bounds__(256) concat_kernel(ConcatArgs a) {
   const int total3 = n3 > 0 ? a.dst3[ib + n3 - 1] + a.size3[ib + n3 - 1] : 0;
   if (blockIdx.x == 0 && threadIdx.x == 0) a.valid[g] = a.copy_rows1 + total2 + total3;
   const int units1 = (a.copy_rows1 + kUnit - 1) / kUnit;
-  const int n_units = units1 + n2 + n3;
   const int sub = threadIdx.x >> 7, lane128 = threadIdx.x & 127;   // two units per pass, 128 pieces each
   const int row_in_unit = lane128 >> 4, piece = lane128 & 15;
-  for (int u = blockIdx.x * 2 + sub; u < n_units; u += gridDim.x * 2) {
-    const uint4 *ks, *vs;
-    int64_t src_row, dst_row;
-    int valid_rows;
-    if (u < units1) {
-      src_row = (int64_t)u * kUnit;
-      dst_row = src_row;
-      valid_rows = min(kUnit, a.copy_rows1 - u * kUnit);
-      ks = a.k1 + (int64_t)g * a.len1 * kPiecesPerRow;
-      vs = a.v1 + (int64_t)g * a.len1 * kPiecesPerRow;
-    } else if (u < units1 + n2) {
-      const int j = u - units1;
-      src_row = a.idx2[ib + j];
-      dst_row = a.copy_rows1 + a.dst2[ib + j];
-      valid_rows = a.size2[ib + j];
-      ks = a.k2 + (int64_t)g * a.len2 * kPiecesPerRow;
-      vs = a.v2 + (int64_t)g * a.len2 * kPiecesPerRow;
-    } else {
-      const int j = u - units1 - n2;
-      src_row = (int64_t)a.idx3[ib + j] * kUnit;
-      dst_row = a.copy_rows1 + total2 + a.dst3[ib + j];
-      valid_rows = a.size3[ib + j];
-      ks = a.k3 + (int64_t)g * a.len3_units * kUnit * kPiecesPerRow;
-      vs = a.v3 + (int64_t)g * a.len3_units * kUnit * kPiecesPerRow;
-    }
+  auto copy_unit = [&](const uint4* ks, const uint4* vs, int64_t src_row, int64_t dst_row, int valid_rows) {
     if (row_in_unit < valid_rows && src_row >= 0 && dst_row + row_in_unit < a.buffer_rows) {
       const int64_t s = (src_row + row_in_unit) * kPiecesPerRow + piece;
       const int64_t d = ((int64_t)g * a.buffer_rows + dst_row + row_in_unit) * kPiecesPerRow + piece;
       a.kd[d] = ks[s];
       a.vd[d] = vs[s];
+    }
+  };
+  // units of src2: only the first `ctas2` CTAs of a group take part (pages in pinned host memory cross PCIe, where a
+  // few CTAs keep the link full and a shallow request queue keeps other kernels' reads of pinned words fast)
+  if ((int)blockIdx.x < a.ctas2) {
+    const uint4* ks = a.k2 + (int64_t)g * a.len2 * kPiecesPerRow;
+    const uint4* vs = a.v2 + (int64_t)g * a.len2 * kPiecesPerRow;
+    for (int j = blockIdx.x * 2 + sub; j < n2; j += a.ctas2 * 2)
+      copy_unit(ks, vs, a.idx2[ib + j], a.copy_rows1 + a.dst2[ib + j], a.size2[ib + j]);
+  }
+  // rows of src1 and units of src3: every CTA, starting with the CTAs that have no units of src2 to move
+  const int n13 = units1 + n3;
+  const int first = (blockIdx.x + gridDim.x - a.ctas2 % gridDim.x) % gridDim.x;
+  for (int u = first * 2 + sub; u < n13; u += gridDim.x * 2) {
+    if (u < units1) {
+      copy_unit(a.k1 + (int64_t)g * a.len1 * kPiecesPerRow, a.v1 + (int64_t)g * a.len1 * kPiecesPerRow, (int64_t)u * kUnit,
+                (int64_t)u * kUnit, min(kUnit, a.copy_rows1 - u * kUnit));
+    } else {
+      const int j = u - units1;
+      copy_unit(a.k3 + (int64_t)g * a.len3_units * kUnit * kPiecesPerRow, a.v3 + (int64_t)g * a.len3_units * kUnit * kPiecesPerRow,
+                (int64_t)a.idx3[ib + j] * kUnit, a.copy_rows1 + total2 + a.dst3[ib + j], a.size3[ib + j]);
     }
   }
 }
@@ -159,6 +156,10 @@ extern "C" int ri_gather_copy_and_concat(const void* key_data1, const void* key_
   a.valid = valid_lengths;
   a.len1 = data_length1; a.len2 = data_length2; a.len3_units = data_length3; a.buffer_rows = buffer_length;
   a.index_length = offset_length; a.copy_rows1 = copy_vectors1;
+  cudaPointerAttributes attr;
+  const bool host_pages = cudaPointerGetAttributes(&attr, key_data2) == cudaSuccess && attr.type == cudaMemoryTypeHost;
+  (void)cudaGetLastError();
+  a.ctas2 = host_pages ? 2 : 16;
   concat_kernel<<<dim3(16, groups), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   RI_LAUNCH_OK("concat_kernel");
   return RI_OK;
