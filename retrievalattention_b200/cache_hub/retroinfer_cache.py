@@ -569,7 +569,7 @@ class retroinfer_cache(KV_Cache):
         layer, wb = self._layers[layer_idx], self.wave_buffer[layer_idx]
         dev = self.layer_mapping[str(layer_idx)]
         per = self._per_device[dev]
-        g, d, gs = self.batch_groups, self.head_dim, self.group_size
+        g, gs = self.batch_groups, self.group_size
         main = torch.cuda.current_stream(dev)
         if out is None:
             out = torch.empty_like(queries)

@@ -35,11 +35,13 @@ class WaveBufferCPU:
         if not self._h:
             raise ValueError(_lib.lib.ri_last_error().decode())
         self._keep = []
+        self._destroy = _lib.lib.ri_wb_destroy      # bound now: module globals may be gone at interpreter exit
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
-            _lib.lib.ri_wb_destroy(h)
+        destroy = getattr(self, "_destroy", None)
+        if h and destroy is not None:
+            destroy(h)
 
     def set_indices(self, hit_block_ids, hit_block_sizes, hit_block_sizes_cumsum, hit_block_nums, miss_block_ids,
                     miss_block_sizes, miss_block_sizes_cumsum, miss_block_nums, update_buffer_indices,
