@@ -39,6 +39,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const uint4* __re
                                                               int pieces, float eps, float inv_dim) {
   __shared__ float warp_sum[kNormThreads / 32];
   __shared__ float s_scale;
+  ri_pdl_enter();
   const int row = blockIdx.x, tid = threadIdx.x;
   const int64_t base = (int64_t)row * pieces;
   float v[kMaxPieces][8];
@@ -92,6 +93,7 @@ template <int DT>
 __global__ void __launch_bounds__(16) rope_split_kernel(const uint4* __restrict__ qkv, const float4* __restrict__ cos_sin,
                                                         const int64_t* __restrict__ positions, uint4* q, uint4* k, uint4* v,
                                                         int q_heads, int kv_heads, int64_t max_positions) {
+  ri_pdl_enter();
   const int row = blockIdx.x, head = blockIdx.y, t = threadIdx.x;
   const int heads = q_heads + 2 * kv_heads;
   const uint4* src = qkv + ((int64_t)row * heads + head) * 16;
@@ -122,6 +124,7 @@ __global__ void __launch_bounds__(16) rope_split_kernel(const uint4* __restrict_
 // in: [rows, 2 * inter] (gate | up), out: [rows, inter]; one 16-byte piece of the output per thread.
 template <int DT>
 __global__ void __launch_bounds__(256) silu_and_mul_kernel(const uint4* __restrict__ in, uint4* out, int pieces, int rows) {
+  ri_pdl_enter();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (int64_t)rows * pieces) return;
   const int64_t row = i / pieces, p = i - row * pieces;
@@ -145,12 +148,11 @@ extern "C" int ri_rmsnorm(const void* d_x, void* d_residual, const void* d_weigh
              "ri_rmsnorm: pointers must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto go = [&](auto kernel) {
-    kernel<<<rows, kNormThreads, 0, s>>>(static_cast<const uint4*>(d_x), static_cast<uint4*>(d_residual),
-                                         static_cast<const uint4*>(d_weight), static_cast<uint4*>(d_out), dim / 8, eps,
-                                         1.0f / (float)dim);
+    return ri_launch_pdl_id(8, kernel, dim3(rows), dim3(kNormThreads), 0, s, static_cast<const uint4*>(d_x),
+                            static_cast<uint4*>(d_residual), static_cast<const uint4*>(d_weight), static_cast<uint4*>(d_out),
+                            dim / 8, eps, 1.0f / (float)dim);
   };
-  if (dtype == RI_BF16) go(rmsnorm_kernel<RI_BF16>); else go(rmsnorm_kernel<RI_F16>);
-  RI_LAUNCH_OK("rmsnorm_kernel");
+  RI_CUDA_OK(dtype == RI_BF16 ? go(rmsnorm_kernel<RI_BF16>) : go(rmsnorm_kernel<RI_F16>));
   return RI_OK;
 }
 
@@ -166,12 +168,11 @@ extern "C" int ri_rope_split(const void* d_qkv, const float* d_cos_sin, const in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(rows, q_heads + 2 * kv_heads);
   auto go = [&](auto kernel) {
-    kernel<<<grid, 16, 0, s>>>(static_cast<const uint4*>(d_qkv), reinterpret_cast<const float4*>(d_cos_sin), d_positions,
-                               static_cast<uint4*>(d_q), static_cast<uint4*>(d_k), static_cast<uint4*>(d_v), q_heads,
-                               kv_heads, max_positions);
+    return ri_launch_pdl_id(8, kernel, grid, dim3(16), 0, s, static_cast<const uint4*>(d_qkv),
+                            reinterpret_cast<const float4*>(d_cos_sin), d_positions, static_cast<uint4*>(d_q),
+                            static_cast<uint4*>(d_k), static_cast<uint4*>(d_v), q_heads, kv_heads, max_positions);
   };
-  if (dtype == RI_BF16) go(rope_split_kernel<RI_BF16>); else go(rope_split_kernel<RI_F16>);
-  RI_LAUNCH_OK("rope_split_kernel");
+  RI_CUDA_OK(dtype == RI_BF16 ? go(rope_split_kernel<RI_BF16>) : go(rope_split_kernel<RI_F16>));
   return RI_OK;
 }
 
@@ -185,9 +186,9 @@ extern "C" int ri_silu_and_mul(const void* d_in, void* d_out, int32_t rows, int3
   const int64_t n = (int64_t)rows * pieces;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   auto go = [&](auto kernel) {
-    kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(d_in), static_cast<uint4*>(d_out), pieces, rows);
+    return ri_launch_pdl_id(8, kernel, dim3(blocks), dim3(256), 0, s, static_cast<const uint4*>(d_in),
+                            static_cast<uint4*>(d_out), pieces, rows);
   };
-  if (dtype == RI_BF16) go(silu_and_mul_kernel<RI_BF16>); else go(silu_and_mul_kernel<RI_F16>);
-  RI_LAUNCH_OK("silu_and_mul_kernel");
+  RI_CUDA_OK(dtype == RI_BF16 ? go(silu_and_mul_kernel<RI_BF16>) : go(silu_and_mul_kernel<RI_F16>));
   return RI_OK;
 }

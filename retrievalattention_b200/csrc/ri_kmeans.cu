@@ -657,11 +657,13 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
     aa.group_stride = N;
     aa.idesc = idesc_f16(DT, kTileM, kTileN);
     {
-      // blocks per CTA: enough CTAs for about a dozen waves over the SMs, at most 16 blocks each
+      // blocks per CTA: enough CTAs for about six waves over the SMs, at most 16 blocks each (config 2: 16 blocks in
+      // both the segmented and the last iteration, an even split of 32 and 512 blocks; 9 blocks per CTA with a dozen
+      // waves left one CTA in four with 5 blocks and cost 2 % of the build)
       WideArgs wa;
       wa.a = aa;
       const int n_blocks = (n_tok + 2 * kTileM - 1) / (2 * kTileM);
-      int per = (int)(((int64_t)n_blocks * problems) / (148 * 12));
+      int per = (int)(((int64_t)n_blocks * problems) / (148 * 6));
       per = per < 1 ? 1 : (per > 16 ? 16 : per);
       wa.blocks_per_cta = per;
       dim3 wgrid((n_blocks + per - 1) / per, problems);
