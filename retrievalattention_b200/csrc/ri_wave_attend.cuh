@@ -443,9 +443,10 @@ __device__ __forceinline__ void attend_group(const AttendArgs& a, const int g, c
 
   // ---- merge the partial results of the group's CTAs through distributed shared memory: this CTA
   //      finishes values [cl * share, (cl+1) * share) of the gs*128 outputs ----
-  const int share = gs * RI_HEAD_DIM / cpg;
+  const int share = (gs * RI_HEAD_DIM + cpg - 1) / cpg;
   for (int tv = tid; tv < share; tv += kThreads) {
     const int v = cl * share + tv, h = v >> 7, ch = v & 127;
+    if (v >= gs * RI_HEAD_DIM) break;      // cluster sizes that do not divide the outputs: the last CTA's share is short
     float mc[cpg], lc[cpg], oc[cpg];
 #pragma unroll
     for (int c = 0; c < cpg; ++c) {

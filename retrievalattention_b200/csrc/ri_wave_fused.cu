@@ -29,8 +29,11 @@ constexpr int kFusedRingBytes = kFusedWarps * kStages * kStageBytes;    // 192 K
 
 template <int CL>
 struct Geom {
-  static constexpr int kMaxSlice = kFusedMaxCentroids / CL;          // centroids a CTA's slice holds at most
-  static constexpr int kKeys = kMaxSlice / kFusedThreads;            // keys per thread: 8 (CL 4) or 4 (CL 8)
+  // centroids a CTA's slice holds at most: 1024 with 8 CTAs per group, 2048 with 4 to 7 (a slice of 8192 / 7 fills
+  // 147 of the 256 threads' runs of keys; the rest hold nothing)
+  static constexpr int kMaxSlice = CL >= 8 ? kFusedMaxCentroids / 8 : kFusedMaxCentroids / 4;
+  static constexpr int kKeys = kMaxSlice / kFusedThreads;            // keys per thread: 8 (CL 4..7) or 4 (CL 8)
+  static_assert(CL >= 4 && CL <= 8, "clusters of 4 to 8 CTAs");
   // floats per head in shared memory: four words of padding after every 32 (see score_at), eight more between heads
   static constexpr int kScoreStride = kMaxSlice + kMaxSlice / 8 + 8;
   static_assert(kKeys == 4 || kKeys == 8, "a thread's keys are loaded as one or two 16-byte pieces");
@@ -785,18 +788,6 @@ int dynamic_budget(int* out, int* sms_out) {
 
 int g_cap_limit = -1;   // ri_wave_test_local_cap
 
-int sm_count(int* out) {
-  static int cached[64] = {0};
-  int dev = 0;
-  RI_CUDA_OK(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && cached[dev] > 0) { *out = cached[dev]; return RI_OK; }
-  int sms = 0;
-  RI_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (dev >= 0 && dev < 64) cached[dev] = sms;
-  *out = sms;
-  return RI_OK;
-}
-
 template <int DT, int CL>
 int launch(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
   FusedArgs f;
@@ -847,14 +838,58 @@ extern "C" int ri_wave_test_local_cap(int cap) {
   return RI_OK;
 }
 
-int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
-  // cluster size: the largest of 8 and 4 CTAs per group whose grid still fits the SMs at one CTA each
-  int sms = 0;
-  const int rc = sm_count(&sms);
+// How many clusters of CL CTAs of this kernel the device can hold at once (asked once per device).  Clusters are placed
+// inside one GPC, so this is less than SMs / CL: a B200 with 148 SMs holds 15 clusters of 8, not 18.
+template <int DT, int CL>
+int resident_clusters(int* out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  RI_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) { *out = cached[dev]; return RI_OK; }
+  int budget = 0, sms = 0;
+  const int rc = dynamic_budget<DT, CL>(&budget, &sms);
   if (rc != RI_OK) return rc;
-  const bool wide = p.groups * 8 <= sms;
-  if (p.dtype == RI_BF16) return wide ? launch<RI_BF16, 8>(p, L, s, gather) : launch<RI_BF16, 4>(p, L, s, gather);
-  return wide ? launch<RI_F16, 8>(p, L, s, gather) : launch<RI_F16, 4>(p, L, s, gather);
+  RI_CUDA_OK(cudaFuncSetAttribute(wave_fused_kernel<DT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CL, 64);
+  cfg.blockDim = dim3(kFusedThreads);
+  cfg.dynamicSmemBytes = (size_t)budget;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, wave_fused_kernel<DT, CL>, &cfg) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    n = sms / CL;               // the query is unavailable: the bound that ignores GPC boundaries
+  }
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  *out = n;
+  return RI_OK;
+}
+
+template <int DT>
+int launch_fused_dt(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
+  // cluster size: the largest of 8 .. 4 CTAs per group with which all groups' clusters are resident at once (a cluster
+  // that has to wait for another one to finish doubles the layer's time).  Clusters are placed inside a GPC, so the
+  // counts are not SMs / size: a B200 holds 15 clusters of 8 or 7 CTAs, 22 of 6, 26 of 5, 33 of 4.
+  int fit = 0, rc;
+  if ((rc = resident_clusters<DT, 8>(&fit)) != RI_OK) return rc;
+  if (p.groups <= fit) return launch<DT, 8>(p, L, s, gather);
+  if ((rc = resident_clusters<DT, 7>(&fit)) != RI_OK) return rc;
+  if (p.groups <= fit) return launch<DT, 7>(p, L, s, gather);
+  if ((rc = resident_clusters<DT, 6>(&fit)) != RI_OK) return rc;
+  if (p.groups <= fit) return launch<DT, 6>(p, L, s, gather);
+  if ((rc = resident_clusters<DT, 5>(&fit)) != RI_OK) return rc;
+  if (p.groups <= fit) return launch<DT, 5>(p, L, s, gather);
+  return launch<DT, 4>(p, L, s, gather);
+}
+
+int launch_fused(const ri_wave_layer& p, const Layout& L, cudaStream_t s, const ri_wave_gather* gather) {
+  return p.dtype == RI_BF16 ? launch_fused_dt<RI_BF16>(p, L, s, gather) : launch_fused_dt<RI_F16>(p, L, s, gather);
 }
 
 int launch_gather_wait(const ri_wave_gather& g, cudaStream_t s) {

@@ -22,9 +22,16 @@ CASES = {
     "tight_budget": Case(1, 2, 4, 2048 + 68, 64, 1, 8, 14, seed=7, buffer_pages=9),
     "empty_clusters": Case(1, 2, 4, 1024 + 68, 64, 1, 4, 15, seed=8, duplicate_rows=37),
     "cfg0_geometry": Case(1, 8, 4, 8192, 512, 1, 9, 118, seed=0, iters=3),
-    # 19 groups and more: the single kernel runs with 4-CTA clusters (below: 8-CTA clusters)
+    # the cluster size follows the number of groups (the largest of 8 .. 4 CTAs with which all clusters are resident
+    # at once; a B200 holds 15 clusters of 8 or 7 CTAs, 22 of 6, 26 of 5, 33 of 4): 20 and 21 groups run with 6
     "many_groups_gs8": Case(5, 4, 8, 1024 + 68, 64, 1, 4, 15, seed=9),
     "many_groups_gs3": Case(7, 3, 3, 1536 + 68, 96, 2, 5, 22, seed=10),
+    # 16 groups (6 CTAs: slices of 8192 / 6 centroids that are not all alike — here some CTAs have no centroid at
+    # all — and 640 or 384 output values shared out over 6 CTAs), 24 groups (5 CTAs), 30 groups (4 CTAs)
+    "sixteen_groups_gs5": Case(2, 8, 5, 2048 + 68, 128, 2, 6, 29, seed=11),
+    "sixteen_groups_gs3": Case(4, 4, 3, 1024 + 68, 64, 1, 4, 15, seed=12),
+    "twentyfour_groups_gs7": Case(3, 8, 7, 1536 + 68, 96, 2, 5, 22, seed=13),
+    "thirty_groups_gs4": Case(5, 6, 4, 1024 + 68, 64, 1, 4, 15, seed=14),
 }
 
 
