@@ -84,11 +84,22 @@ __device__ __forceinline__ void argmax32(const uint32_t (&r)[32], int col_base, 
   const float a0 = max3(m11[0], m11[1], m11[2]), a1 = max3(m11[3], m11[4], m11[5]), a2 = max3(m11[6], m11[7], m11[8]);
   const float m = max3(max3(a0, a1, a2), m11[9], m11[10]);
   if (m > best) {          // strict: an equal value in a later column never replaces an earlier one
-    uint32_t mask = 0;
+    // First column equal to the maximum, found on the FMA pipe (the compare-and-mask form of this search kept the
+    // ALU pipe, which also does every maximum, busier than the tensor pipe whenever a problem has few centroid
+    // tiles): v - m is exactly 0 for the maxima and negative elsewhere, so fma(v - m, 2^120, -i) is -i for them and
+    // far below -32 for the others (differences under 2^-115 do not occur between scores of ordinary magnitude);
+    // the maximum of those is minus the first index.
+    float w[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) mask |= (v[i] == m ? 1u : 0u) << i;
+    for (int i = 0; i < 32; ++i) w[i] = fmaf(v[i] - m, 0x1p120f, -(float)i);
+    float t11[11];
+#pragma unroll
+    for (int i = 0; i < 10; ++i) t11[i] = max3(w[3 * i], w[3 * i + 1], w[3 * i + 2]);
+    t11[10] = fmaxf(w[30], w[31]);
+    const float b0 = max3(t11[0], t11[1], t11[2]), b1 = max3(t11[3], t11[4], t11[5]), b2 = max3(t11[6], t11[7], t11[8]);
+    const float wm = max3(max3(b0, b1, b2), t11[9], t11[10]);
     best = m;
-    best_idx = col_base + __ffs((int)mask) - 1;
+    best_idx = col_base + (int)(-wm);
   }
 }
 
