@@ -286,6 +286,205 @@ kmeans_assign_wide_kernel(const __grid_constant__ CUtensorMap map_keys, const __
   }
 }
 
+// ---- assign kernel, centroids resident ----------------------------------------------------------------
+// Problems of at most 512 centroids (the segmented iterations of the reference's schedule, the re-index build): the
+// problem's centroid tiles (up to four, 128 KB) are fetched ONCE per CTA and stay in shared memory, and only the
+// tokens stream, as single 128-row tiles through a three-slot ring (the wide kernel above re-fetches the centroid
+// tiles for every 256 tokens).  Per token tile two rounds of two centroid tiles each (accumulators: 2 buffers x
+// 2 centroid tiles x 128 columns); the eight epilogue warps are four lane quarters x the two centroid tiles of a
+// round, so a token's running arg-max lives in two warps, which meet through shared memory once per token tile
+// (equal maxima: the lower index wins, as within a warp).  Every warp runs a fixed number of token tiles and rounds
+// whatever its waits return, so the named barrier of that merge is always reached.
+// Measured on a segmented launch of configuration 2 (ncu): 580 us and the tensor pipe 48 % active, against 610 us /
+// 45 % for the wide kernel; with the epilogue's tcgen05.ld removed 388 us / 70 %, with a single 32-column load per
+// warp and round left 527 us / 52 % — the loads themselves, not the arithmetic behind them, hold the MMAs up; four
+// accumulator buffers of one centroid tile (the issuer three rounds ahead) were slower still (647 us).
+constexpr int kResSlots = 3;
+constexpr int kResSmem = 1024 /*align*/ + 4 * 2 * kHalfBytes /*B: 4 tiles*/ + kResSlots * 2 * kHalfBytes /*A ring*/ + 256;
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+kmeans_assign_resident_kernel(const __grid_constant__ CUtensorMap map_keys, const __grid_constant__ CUtensorMap map_cent,
+                              WideArgs w) {
+  const AssignArgs& a = w.a;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sB = base;                                         // [centroid tile][K half]
+  const uint32_t sA = base + 4 * 2 * kHalfBytes;                    // [slot][K half]
+  const uint32_t bars = sA + kResSlots * 2 * kHalfBytes;
+  auto bar_a_full = [&](int s) { return bars + 8u * s; };
+  auto bar_a_empty = [&](int s) { return bars + 8u * (kResSlots + s); };
+  const uint32_t bar_b_full = bars + 8u * (2 * kResSlots);
+  auto bar_acc_full = [&](int b) { return bars + 8u * (2 * kResSlots + 1 + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (2 * kResSlots + 3 + b); };
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort, s_skip;
+  __shared__ float s_best[2][kTileM];      // the merge of a token's two warps (indices fit 16 bits: <= 512 centroids)
+  __shared__ uint16_t s_idx[2][kTileM];
+
+  if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(a.error_flag);
+  __syncthreads();
+  if (s_skip) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int problem = blockIdx.y;
+  const int units_total = (a.n_tok + kTileM - 1) / kTileM;
+  const int first_unit = blockIdx.x * w.blocks_per_cta * 2;
+  const int nu = min(w.blocks_per_cta * 2, units_total - first_unit);       // > 0 by the grid's construction
+  const int64_t tok_row0 = (int64_t)(problem / a.seg_per_group) * a.group_stride +
+                           (int64_t)(problem % a.seg_per_group) * a.n_tok + (int64_t)first_unit * kTileM;
+  const int cen_row0 = problem * a.n_cen;
+  const int n_tiles = (a.n_cen + kTileN - 1) / kTileN;              // 1 .. 4
+  const int rounds = (n_tiles + 1) / 2;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kResSlots; ++s) { mbar_init(bar_a_full(s), 1); mbar_init(bar_a_empty(s), 1); }
+    mbar_init(bar_b_full, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(kWideTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar_b_full, n_tiles * 2 * kHalfBytes);
+      for (int t = 0; t < n_tiles; ++t) {
+        tma_load_2d(sB + t * 2 * kHalfBytes, &map_cent, bar_b_full, 0, cen_row0 + t * kTileN);
+        tma_load_2d(sB + t * 2 * kHalfBytes + kHalfBytes, &map_cent, bar_b_full, 64, cen_row0 + t * kTileN);
+      }
+      int issued = 0;
+      bool ok = true;
+      for (int u = 0; ok && u < nu; ++u) {
+        const int s = u % kResSlots;
+        ok = mbar_wait(bar_a_empty(s), ((u / kResSlots) & 1) ^ 1, abort_flag, 21);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_a_full(s), 2 * kHalfBytes);
+        const int row = (int)(tok_row0 + (int64_t)u * kTileM);
+        tma_load_2d(sA + s * 2 * kHalfBytes, &map_keys, bar_a_full(s), 0, row);
+        tma_load_2d(sA + s * 2 * kHalfBytes + kHalfBytes, &map_keys, bar_a_full(s), 64, row);
+        issued = u + 1;
+      }
+      if (*abort_flag) {
+        // give our own copies still in flight a bounded chance to land before the CTA exits
+        mbar_wait(bar_b_full, 0, abort_flag, 26);
+        for (int u = max(0, issued - kResSlots); u < issued; ++u)
+          mbar_wait(bar_a_full(u % kResSlots), (u / kResSlots) & 1, abort_flag, 27);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait(bar_b_full, 0, abort_flag, 22);
+      int j = 0;                       // rounds issued so far (accumulator buffer = j & 1)
+      for (int u = 0; ok && u < nu; ++u) {
+        const int s = u % kResSlots;
+        ok = mbar_wait(bar_a_full(s), (u / kResSlots) & 1, abort_flag, 23);
+        for (int r = 0; ok && r < rounds; ++r, ++j) {
+          const int buf = j & 1;
+          ok = mbar_wait(bar_acc_empty(buf), ((j >> 1) & 1) ^ 1, abort_flag, 24);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int ct = 2 * r + h;
+            if (ct < n_tiles) {
+              const uint32_t d_tmem = tmem_base + buf * 2 * kTileN + h * kTileN;
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb) {
+                const uint64_t da = umma_desc_sw128(sA + (s * 2 + kb) * kHalfBytes);
+                const uint64_t db = umma_desc_sw128(sB + (ct * 2 + kb) * kHalfBytes);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tc_mma_f16(d_tmem, da + 2 * k, db + 2 * k, a.idesc, (kb | k) != 0);
+              }
+            }
+          }
+          tc_commit(bar_acc_full(buf));
+        }
+        if (ok) tc_commit(bar_a_empty(s));   // the token tile is free once all its MMAs have read it
+      }
+    }
+  } else {
+    // ---------------- epilogue: running arg-max, two warps per token ----------------
+    const int half = (warp - 2) >> 2;                // which centroid tile of a round
+    const int lane_group = warp & 3;                 // TMEM lanes 32*lane_group .. +31 (a warp may touch only its quarter)
+    const int row = lane_group * 32 + lane;          // this lane's token within the tile
+    int j = 0;
+    bool ok = true;
+    for (int u = 0; u < nu; ++u) {                   // fixed trip counts: the barrier below must be reached by all
+      float best = -INFINITY;
+      int best_idx = 0;
+      for (int r = 0; r < rounds; ++r, ++j) {
+        const int buf = j & 1;
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(bar_acc_full(buf), (j >> 1) & 1, abort_flag, 25));   // warp-uniform
+        const int ct = 2 * r + half;
+        if (ok && ct < n_tiles) {
+          tc_fence_after();
+          const int col0 = ct * kTileN;
+          const int valid = min(kTileN, a.n_cen - col0);
+          const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * 2 * kTileN + half * kTileN;
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tc_ld32(taddr, r0);
+          tc_ld32(taddr + 32, r1);
+          tc_wait_ld();
+          tc_ld_landed(r0);
+          tc_ld_landed(r1);
+          tc_ld32(taddr + 64, r2);
+          tc_ld32(taddr + 96, r3);
+          if (valid == kTileN) {
+            argmax32<true>(r0, col0, 32, best, best_idx);
+            argmax32<true>(r1, col0 + 32, 32, best, best_idx);
+            tc_wait_ld();
+            tc_ld_landed(r2);
+            tc_ld_landed(r3);
+            argmax32<true>(r2, col0 + 64, 32, best, best_idx);
+            argmax32<true>(r3, col0 + 96, 32, best, best_idx);
+          } else {
+            argmax32<false>(r0, col0, valid, best, best_idx);
+            argmax32<false>(r1, col0 + 32, valid - 32, best, best_idx);
+            tc_wait_ld();
+            tc_ld_landed(r2);
+            tc_ld_landed(r3);
+            argmax32<false>(r2, col0 + 64, valid - 64, best, best_idx);
+            argmax32<false>(r3, col0 + 96, valid - 96, best, best_idx);
+          }
+          tc_fence_before();
+        }
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(bar_acc_empty(buf));
+      }
+      // the two warps of a token meet (buffers alternate per token tile, so one barrier per tile is enough)
+      const int par = u & 1;
+      if (half == 1) { s_best[par][row] = best; s_idx[par][row] = (uint16_t)best_idx; }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0) {
+        const float ob = s_best[par][row];
+        const int oi = (int)s_idx[par][row];
+        if (ob > best || (ob == best && oi < best_idx)) best_idx = oi;
+        const int local_tok = (first_unit + u) * kTileM + row;
+        if (ok && local_tok < a.n_tok) a.assign[tok_row0 + (int64_t)u * kTileM + row] = best_idx;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_abort) *a.error_flag = s_abort;   // which wait gave up (see mbar_wait call sites)
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kWideTmemCols));
+  }
+}
+
 // ---- centre ---------------------------------------------------------------------------------
 constexpr int kMeanRows = 2048;   // rows per partial-sum CTA
 
@@ -656,6 +855,7 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
   rc = make_row_map(&map_cent, cent, (int64_t)Z * C, DT);
   if (rc != RI_OK) return rc;
   RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem));
+  RI_CUDA_OK(cudaFuncSetAttribute(kmeans_assign_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kResSmem));
 
   for (int it = 0; it < p->n_iters; ++it) {
     const bool last = it == p->n_iters - 1;
@@ -678,8 +878,13 @@ int run_fit(const ri_kmeans* p, const FitLayout& L, const void* centred, cudaStr
       per = per < 1 ? 1 : (per > 16 ? 16 : per);
       wa.blocks_per_cta = per;
       dim3 wgrid((n_blocks + per - 1) / per, problems);
-      kmeans_assign_wide_kernel<<<wgrid, kWideThreads, kWideSmem, s>>>(map_keys, map_cent, wa);
-      RI_LAUNCH_OK("kmeans_assign_wide_kernel");
+      if (n_cen <= 4 * kTileN) {        // the problem's centroids fit shared memory: they stay there
+        kmeans_assign_resident_kernel<<<wgrid, kWideThreads, kResSmem, s>>>(map_keys, map_cent, wa);
+        RI_LAUNCH_OK("kmeans_assign_resident_kernel");
+      } else {
+        kmeans_assign_wide_kernel<<<wgrid, kWideThreads, kWideSmem, s>>>(map_keys, map_cent, wa);
+        RI_LAUNCH_OK("kmeans_assign_wide_kernel");
+      }
     }
 
     BucketArgs ba;
