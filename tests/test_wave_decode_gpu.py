@@ -32,6 +32,9 @@ CASES = {
     "sixteen_groups_gs3": Case(4, 4, 3, 1024 + 68, 64, 1, 4, 15, seed=12),
     "twentyfour_groups_gs7": Case(3, 8, 7, 1536 + 68, 96, 2, 5, 22, seed=13),
     "thirty_groups_gs4": Case(5, 6, 4, 1024 + 68, 64, 1, 4, 15, seed=14),
+    # the fp16 instantiations (one small group count, one that runs with 6-CTA clusters)
+    "fp16_gs4": Case(2, 2, 4, 2048 + 68, 128, 1, 6, 30, seed=15, dtype=torch.float16),
+    "fp16_sixteen_groups": Case(4, 4, 2, 1024 + 68, 64, 1, 4, 15, seed=16, dtype=torch.float16),
 }
 
 
