@@ -1,5 +1,5 @@
-// The whole decode step of one layer in ONE kernel: a thread-block cluster per group (CL = 4 or 8 CTAs of
-// 256 threads, one CTA per SM) runs
+// The whole decode step of one layer in ONE kernel: a thread-block cluster per group (CL = 4 .. 8 CTAs of
+// 256 threads, one CTA per SM; the host picks the largest size with which all clusters are resident at once) runs
 //   phase 1  scan    s = alpha * q.C^T over the group's centroids (each CTA one slice, streamed
 //                    through the lane-private cp.async ring), per-CTA softmax partials exchanged
 //                    through distributed shared memory;
