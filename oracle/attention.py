@@ -7,7 +7,10 @@ pin) is not available.  The arithmetic below is flash decoding with a per-key
 weight on the softmax denominator, which is what the operands at the two call
 sites imply (cache_hub/retroinfer_cache.py:611-617: key = centroid, value =
 per-cluster value SUM, weight = cluster size; :666-674: exact keys/values, merge
-with a previous (out, lse) pair), evaluated in fp32.
+with a previous (out, lse) pair), evaluated in fp32.  What can be checked is checked against the
+flash-attn library the operator was forked from (tests/test_oracle_attention_gpu.py): the
+unweighted case, the merge, and the weighted case as attention over tokens that carry their
+centroid as key.
 """
 from __future__ import annotations
 
