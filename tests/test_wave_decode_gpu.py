@@ -230,3 +230,41 @@ def test_invalid_arguments_are_rejected():
     p = _lib.WaveLayer()
     assert _lib.lib.ri_wave_decode_layer(C.byref(p), None) == -1
     assert b"groups" in _lib.lib.ri_last_error()
+
+
+def _random_case(seed: int) -> Case:
+    """A geometry drawn at random: 1 .. 40 groups (every cluster size of the single kernel), every group size, centroid
+    counts that do not divide evenly over 5, 6 or 7 CTAs."""
+    rng = torch.Generator().manual_seed(1000 + seed)
+    pick = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=rng))   # noqa: E731
+    batch, kv_heads = pick(1, 8), pick(1, 5)
+    n_segment = pick(1, 2)
+    n_centroids = 8 * n_segment * pick(4, 12)
+    nprobe = pick(2, 6)
+    return Case(batch, kv_heads, pick(1, 8), 68 + 16 * n_centroids + 8 * pick(0, 40), n_centroids, n_segment, nprobe,
+                pick(0, n_centroids // 3), seed=100 + seed)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_geometries_single_kernel_against_oracle_and_stages(seed):
+    case = _random_case(seed)
+    cpu = build_cpu_index(case)
+    static_len = SINK + RECENT
+    q = queries(case)
+    ref_out, parts = run_oracle(case, cpu, q, static_len)
+    layer = to_gpu_layer(case, cpu, static_len)
+    out = layer.compute(q.cuda()).clone()
+    ret, est = layer.retrieved_ids.cpu().clone(), layer.estimated_ids.cpu().clone()
+    staged = layer.compute_staged(q.cuda()).clone()
+    plain = to_gpu_layer(case, cpu, static_len, want_ids=False).compute(q.cuda())
+    torch.cuda.synchronize()
+    what = (case.groups, case.group_size, case.n_centroids, case.nprobe, case.n_estimate)
+    assert oss.selection_matches(parts["dist"], ret, case.nprobe), what
+    if case.n_estimate:
+        assert oss.selection_matches(parts["dist"], torch.cat((ret, est), dim=1), case.nprobe + case.n_estimate), what
+    for name, o in (("single kernel", out), ("stages", staged), ("output only", plain)):
+        err = (o.cpu().float() - ref_out.float()).abs()
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3, (name, what, float(err.max()), float(err.mean()))
+    # the three forms sum in different orders: they may differ by a rounding step of the 16-bit output or two
+    for other in (staged, plain):
+        assert ((out.float() - other.float()).abs() <= 2.0 ** -6 * out.float().abs().clamp_min(0.5)).all(), what
