@@ -103,6 +103,11 @@ BF16_CASES = {
     "one_iteration": (2, 4000, 256, 4, 1, 5),
     "two_iterations": (2, 4000, 256, 4, 2, 6),
     "two_iterations_wide": (1, 6000, 1024, 2, 2, 7),
+    # centroid tiles of the resident-centroid kernel: three tiles (two rounds, the second with one tile), a partial
+    # second tile, a partial third tile, token counts that are no multiple of 128
+    "three_tiles": (2, 3000, 384, 1, 2, 8),
+    "partial_second_tile": (2, 2600, 224, 1, 2, 9),
+    "partial_third_tile": (1, 2053, 352, 1, 1, 10),
     # configuration 0 of the benchmark: 8 kv heads x (8192 - 68) clustered keys, 512 centroids, 10 iterations
     "cfg0_geometry": (8, 8192 - 68, 512, 1, 10, 0),
 }
