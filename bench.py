@@ -683,7 +683,7 @@ def run_cfg4(args, rank, world, local_rank, device, dist, cpu_group, log):
     return out
 
 
-def run_host_tier(geo, args, log):
+def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
     """``--kv-on-host``: the configuration's geometry with the cluster store in pinned host memory and an LRU page cache
     on the GPU (the reference's tiers), ``--layers`` of its layers (pinned memory is the limit), eager stepping (the host
     takes part in every layer).  Two query streams: fresh Gaussian queries every step (no temporal locality: the worst
@@ -694,8 +694,17 @@ def run_host_tier(geo, args, log):
     ahead, the host-staged copy, and the reference's own pattern."""
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        # several GPUs: the batch is split over the ranks, which do not exchange anything (every rank has its own
+        # PCIe link, host threads and page caches); gloo carries the barriers and the sums
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+        if geo.batch % world:
+            raise SystemExit(f"batch {geo.batch} does not split over {world} ranks")
+        geo = replace(geo, batch=geo.batch // world)
     cfg = geo.index()
     steps, warm = args.steps, max(args.warmup, 3)
     max_new = 8 * (steps + warm) + 4
@@ -714,12 +723,12 @@ def run_host_tier(geo, args, log):
                                      miss_path=path, use_cluster_estimation=path == "pull", **cfg.as_kwargs())
             for l in range(geo.layers):
                 for b in range(geo.batch):
-                    k, v = make_kv(geo.kv_heads, geo.context, 128, seed=l * 1000 + b, theta=geo.rope_theta, device=device)
+                    k, v = make_kv(geo.kv_heads, geo.context, 128, seed=(rank * 131 + l) * 1000 + b, theta=geo.rope_theta, device=device)
                     cache.prefill_update_kv_cache(None, k, v, l, b)
             cache.prepare_cache()
             built = path
             log(f"set-up: {geo.layers} layers indexed, miss path {path}")
-        g = torch.Generator(device=device).manual_seed(5)
+        g = torch.Generator(device=device).manual_seed(5 + rank)
         rnd = lambda h: torch.randn((geo.batch, 1, h, 128), generator=g, device=device).to(torch.bfloat16)   # noqa: E731
         results[mode] = {}
         for name, keep in (("fresh queries", 0.0), ("drifting queries", 0.95)):
@@ -740,25 +749,35 @@ def run_host_tier(geo, args, log):
             for _ in range(warm):
                 step(False)
             torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
             t0 = time.perf_counter()
             for _ in range(steps):
                 step(True)
             torch.cuda.synchronize()
             sec = time.perf_counter() - t0
             hit, miss = pages
-            results[mode][name] = {"tok_s": round(geo.batch * steps / sec, 1), "ms_per_step": round(sec / steps * 1e3, 3),
+            if dist is not None:          # the slowest rank's time, everybody's pages
+                t = torch.tensor([sec], dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                pg = torch.tensor([hit, miss], dtype=torch.int64)
+                dist.all_reduce(pg)
+                sec, hit, miss = float(t[0]), int(pg[0]), int(pg[1])
+            results[mode][name] = {"tok_s": round(geo.batch * world * steps / sec, 1), "ms_per_step": round(sec / steps * 1e3, 3),
                                    "ms_per_layer": round(sec / steps / geo.layers * 1e3, 3),
                                    "page_hit_rate": round(hit / max(hit + miss, 1), 4),
                                    "missed_page_gbs": round(miss * 8 * 128 * 2 * 2 / sec / 1e9, 2)}
             log(f"{mode}, {name}: {results[mode][name]}")
+    if rank != 0:
+        return
     first = next(iter(results))
     main = results[first]["drifting queries"]
     print(json.dumps({
-        "metric": METRIC, "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+        "metric": METRIC, "value": main["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": f"{geo.name}: host tier (cluster store in pinned host memory, GPU page cache of "
-                               f"{cfg.cache_cluster_num} clusters per group), {geo.layers} layers, batch {geo.batch}, ctx {geo.context}, "
+                               f"{cfg.cache_cluster_num} clusters per group), {geo.layers} layers, batch {geo.batch} per GPU, ctx {geo.context}, "
                                f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; value: drifting queries, missed pages by '{first}'",
                    "timing": "wall clock around eager steps (the host takes part in every layer)"},
         "host_tier": results}), flush=True)
@@ -978,8 +997,7 @@ def main():
             run_kmeans(geo, args, log)
         return
     if args.kv_on_host:
-        if rank == 0:
-            run_host_tier(geo, args, log)
+        run_host_tier(geo, args, log, rank, world, local_rank)
         return
     run_decode(geo, args, rank, world, local_rank, log)
     if world > 1:
