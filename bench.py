@@ -2,6 +2,7 @@
 """Decode-throughput benchmark of the wave-index attention path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config cfg1|cfg2|cfg3|cfg4] [--no-model]
+                    [--kv-on-host [--miss-path pull|staged|uva] [--layers L]] [--prefill-seq S] [--no-cfg4]
 
 Workload (default, N=1): Llama-3-8B decode-attention geometry — 32 layers, 32 q / 8 kv heads,
 head_dim 128, batch 4, context 131072, 8192 centroids per kv head, budget 0.018, estimate 0.232 —
@@ -18,7 +19,10 @@ vocabulary head with random weights — around the same caches; ``--no-model`` s
 (the prefill clustering of configuration 2 against the tensor-core roofline).
 
 ``--config cfg2`` times the prefill clustering alone (32 groups x 131072 keys, 8192 centroids,
-10 iterations) in more detail.
+10 iterations) in more detail.  ``--kv-on-host`` times the host tier (cluster store in pinned host memory, page
+cache on the GPU) for every way of bringing missed pages up; under torchrun the batch is split over the ranks.
+``--prefill-seq S`` times the dense prefill attention of one prompt of S tokens alone.  On several GPUs the
+line also carries ``cfg4``: configuration 4 (64q/8kv heads, batch 16) with its KV heads sharded over the ranks.
 """
 from __future__ import annotations
 
