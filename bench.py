@@ -21,7 +21,8 @@ vocabulary head with random weights — around the same caches; ``--no-model`` s
 ``--config cfg2`` times the prefill clustering alone (32 groups x 131072 keys, 8192 centroids,
 10 iterations) in more detail.  ``--kv-on-host`` times the host tier (cluster store in pinned host memory, page
 cache on the GPU) for every way of bringing missed pages up; under torchrun the batch is split over the ranks.
-``--prefill-seq S`` times the dense prefill attention of one prompt of S tokens alone.  On several GPUs the
+``--prefill-seq S`` times the dense prefill attention of one prompt of S tokens alone.  The default line carries a
+short host-tier run as ``host_tier`` (``--no-host-tier`` skips it; a ``--layers`` override does too).  On several GPUs the
 line also carries ``cfg4``: configuration 4 (64q/8kv heads, batch 16) with its KV heads sharded over the ranks.
 """
 from __future__ import annotations
@@ -648,6 +649,22 @@ def run_decode(geo, args, rank, world, local_rank, log):
         result["cfg4"] = c4
         cfgd["cfg4"] = (f"{c4['layers']} of 80 layers: {c4['ms_per_step']} ms/step, {c4['tok_s']} tok/s "
                         f"({c4['tok_s_at_80_layers']} at 80 layers), e2e {c4['e2e_tok_s']}, gather {c4['gather_check']}")
+    if world == 1 and not args.no_host_tier and not args.layers and args.config == "cfg1":
+        # the host tier in short (configuration 3's geometry): the caches of the workload above are released first
+        wl.graph = wl.cache = None
+        del wl
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        ht = result["host_tier"] = host_tier_summary(args, log)
+        best, ref = ht["results"]["pull, one layer ahead"], ht["results"]["uva (the reference's pattern)"]
+        full = GEOMETRIES["cfg3"]
+        at_model = lambda r: round(full.batch / (r["ms_per_layer"] * 1e-3 * full.layers), 1)   # noqa: E731
+        cfgd["host_tier"] = ("cfg3 geometry, 2 layers timed, KV in pinned host memory: "
+                             + "; ".join(f"{k}: {best[k]['ms_per_layer']} ms/layer = {at_model(best[k])} tok/s at the model's "
+                                         f"{full.layers} layers, {best[k]['missed_page_gbs']} GB/s of missed pages (the "
+                                         f"reference's pattern: {ref[k]['ms_per_layer']} ms/layer)"
+                                         for k in ("fresh queries", "drifting queries")))
     if rank == 0:
         print(json.dumps(result), flush=True)
     if world > 1:
@@ -687,36 +704,19 @@ def run_cfg4(args, rank, world, local_rank, device, dist, cpu_group, log):
     return out
 
 
-def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
-    """``--kv-on-host``: the configuration's geometry with the cluster store in pinned host memory and an LRU page cache
-    on the GPU (the reference's tiers), ``--layers`` of its layers (pinned memory is the limit), eager stepping (the host
-    takes part in every layer).  Two query streams: fresh Gaussian queries every step (no temporal locality: the worst
-    case for the page cache) and slowly drifting ones (q_t = 0.95 q_{t-1} + 0.31 noise).  Reports tokens/s, the page
-    cache's hit rate and the host-to-device bytes of the missed pages per second, for every way of bringing the missed
-    pages up (``--miss-path`` picks one): the side-stream pull with the next layer searched and pulled one layer ahead
-    (the next layer's query handed over as ``queries_next``: the best any estimate can do), the same without looking
-    ahead, the host-staged copy, and the reference's own pattern."""
+HOST_TIER_MODES = {"pull, one layer ahead": ("pull", True), "pull": ("pull", False), "staged": ("staged", False),
+                   "uva (the reference's pattern)": ("uva", False)}
+
+
+def host_tier_measure(geo, modes, steps, warm, device, log, rank=0, world=1, dist=None):
+    """Eager decode steps of ``geo`` (one rank's share) on the host tier for each of ``modes`` (name -> (miss path,
+    look ahead)), with fresh Gaussian queries every step (no temporal locality: the worst case for the page cache) and
+    with slowly drifting ones (q_t = 0.95 q_{t-1} + 0.31 noise).  Wall clock (the host takes part in every layer)."""
     from retrievalattention_b200.cache_hub import retroinfer_cache
 
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    dist = None
-    if world > 1:
-        # several GPUs: the batch is split over the ranks, which do not exchange anything (every rank has its own
-        # PCIe link, host threads and page caches); gloo carries the barriers and the sums
-        import torch.distributed as dist
-        dist.init_process_group("gloo")
-        if geo.batch % world:
-            raise SystemExit(f"batch {geo.batch} does not split over {world} ranks")
-        geo = replace(geo, batch=geo.batch // world)
     cfg = geo.index()
-    steps, warm = args.steps, max(args.warmup, 3)
-    max_new = 8 * (steps + warm) + 4
+    max_new = 2 * len(modes) * (steps + warm) + 4
     mapping = {str(l): str(device) for l in range(geo.layers)}
-    modes = {"pull, one layer ahead": ("pull", True), "pull": ("pull", False), "staged": ("staged", False),
-             "uva (the reference's pattern)": ("uva", False)}
-    if args.miss_path:
-        modes = {k: v for k, v in modes.items() if v[0] == args.miss_path}
     results, cache, built = {}, None, None
     for mode, (path, ahead) in modes.items():
         if built != path:
@@ -731,7 +731,7 @@ def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
                     cache.prefill_update_kv_cache(None, k, v, l, b)
             cache.prepare_cache()
             built = path
-            log(f"set-up: {geo.layers} layers indexed, miss path {path}")
+            log(f"host tier set-up: {geo.layers} layers indexed, miss path {path}")
         g = torch.Generator(device=device).manual_seed(5 + rank)
         rnd = lambda h: torch.randn((geo.batch, 1, h, 128), generator=g, device=device).to(torch.bfloat16)   # noqa: E731
         results[mode] = {}
@@ -772,6 +772,35 @@ def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
                                    "page_hit_rate": round(hit / max(hit + miss, 1), 4),
                                    "missed_page_gbs": round(miss * 8 * 128 * 2 * 2 / sec / 1e9, 2)}
             log(f"{mode}, {name}: {results[mode][name]}")
+    cache = None
+    torch.cuda.empty_cache()
+    return results
+
+
+def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
+    """``--kv-on-host``: the configuration's geometry with the cluster store in pinned host memory and an LRU page cache
+    on the GPU (the reference's tiers), ``--layers`` of its layers (pinned memory is the limit), eager stepping.
+    Reports tokens/s, the page cache's hit rate and the host-to-device bytes of the missed pages per second, for every
+    way of bringing the missed pages up (``--miss-path`` picks one): the side-stream pull with the next layer searched
+    and pulled one layer ahead (the next layer's query handed over as ``queries_next``: the best any estimate can do),
+    the same without looking ahead, the host-staged copy, and the reference's own pattern."""
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        # several GPUs: the batch is split over the ranks, which do not exchange anything (every rank has its own
+        # PCIe link, host threads and page caches); gloo carries the barriers and the sums
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+        if geo.batch % world:
+            raise SystemExit(f"batch {geo.batch} does not split over {world} ranks")
+        geo = replace(geo, batch=geo.batch // world)
+    cfg = geo.index()
+    steps, warm = args.steps, max(args.warmup, 3)
+    modes = dict(HOST_TIER_MODES)
+    if args.miss_path:
+        modes = {k: v for k, v in modes.items() if v[0] == args.miss_path}
+    results = host_tier_measure(geo, modes, steps, warm, device, log, rank, world, dist)
     if rank != 0:
         return
     first = next(iter(results))
@@ -785,6 +814,19 @@ def run_host_tier(geo, args, log, rank=0, world=1, local_rank=0):
                                f"{cfg.n_centroids} centroids, nprobe {cfg.nprobe}; value: drifting queries, missed pages by '{first}'",
                    "timing": "wall clock around eager steps (the host takes part in every layer)"},
         "host_tier": results}), flush=True)
+
+
+def host_tier_summary(args, log):
+    """The host tier in short, for the default line: configuration 3's geometry (Qwen2.5-7B, context 262144, batch 8) with
+    2 of its layers, the side-stream pull one layer ahead and the reference's own pattern beside it."""
+    geo = replace(GEOMETRIES["cfg3"], layers=2, name=GEOMETRIES["cfg3"].name + "-2layers")
+    modes = {k: HOST_TIER_MODES[k] for k in ("pull, one layer ahead", "uva (the reference's pattern)")}
+    res = host_tier_measure(geo, modes, 8, 3, torch.device("cuda", 0), log)
+    cfg = geo.index()
+    return {"workload": f"{geo.name}: cluster store in pinned host memory, GPU page cache of {cfg.cache_cluster_num} clusters per "
+                        f"group, batch {geo.batch}, ctx {geo.context}, {cfg.n_centroids} centroids, nprobe {cfg.nprobe}; eager steps, "
+                        "wall clock; fresh queries = no temporal locality, drifting = q_t = 0.95 q_(t-1) + noise",
+            "results": res}
 
 
 def reference_arm(geo, args, log):
@@ -973,6 +1015,7 @@ def main():
                     help="time the host tier of --config (cluster store in pinned host memory, GPU page cache), --layers layers")
     ap.add_argument("--miss-path", default="", choices=["", "pull", "staged", "uva"],
                     help="with --kv-on-host: only this way of bringing missed pages up (default: all, one after the other)")
+    ap.add_argument("--no-host-tier", action="store_true", help="skip the short host-tier run (key host_tier, single GPU)")
     ap.add_argument("--no-cfg4", action="store_true",
                     help="several GPUs: skip the run of configuration 4 (72B geometry, heads sharded) after the main one")
     ap.add_argument("--quick", action="store_true", help="cfg2 only: one warm-up, one repetition (profiler captures)")
